@@ -1,0 +1,70 @@
+// Communicator: one NCCL communicator per wholegraph_comm_ (none when world_size == 1),
+// plus the small host-side collectives the handle and embedding code need.
+// Role of the reference's cpp/src/wholegraph/communicator.cpp:255-810 and nccl_comms.cpp.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+#include <mutex>
+#include <set>
+#include <string>
+#include <vector>
+
+#include <wholegraph/wholegraph.h>
+
+struct wholegraph_handle_;
+
+struct wholegraph_comm_ {
+  int world_rank = 0;
+  int world_size = 1;
+  int dev_id     = 0;
+  void* nccl     = nullptr;  // ncclComm_t; null for a single-rank communicator
+  wholegraph_distributed_backend_t backend = WHOLEGRAPH_DB_NCCL;
+  std::mutex mu;
+  std::set<wholegraph_handle_*> handles;  // freed when the communicator is destroyed
+  int next_handle_id = 0;
+  uint64_t tag       = 0;  // identical on all ranks; names the side-band unix sockets
+
+  // Staging for host-side collectives (1 MiB per rank).
+  cudaStream_t side_stream = nullptr;
+  void* dev_stage          = nullptr;
+  void* pin_stage          = nullptr;
+  size_t stage_bytes       = 0;
+
+  // Second stream on which the row exchange of a distributed op runs while the caller's
+  // stream keeps gathering, and the events that fence the two.
+  cudaStream_t xchg_stream = nullptr;
+  std::vector<cudaEvent_t> events;
+  cudaEvent_t event(size_t i);  // i-th pooled event (created on demand, timing disabled)
+
+  // ---- host collectives (blocking; caller memory is pageable host memory) ----
+  void host_allgather(const void* send, void* recv, size_t bytes_per_rank);
+  void host_alltoall(const void* send, void* recv, size_t bytes_per_pair);
+  void barrier();
+  // True when every rank passed the same bytes.
+  bool all_same(const void* value, size_t bytes);
+
+  // ---- device collectives, asynchronous on `stream` ----
+  // Byte alltoallv: send_counts / recv_counts / displacements in units of `unit_bytes`.
+  void alltoallv(const void* send, const int64_t* send_counts, const int64_t* send_displs,
+                 void* recv, const int64_t* recv_counts, const int64_t* recv_displs,
+                 size_t unit_bytes, cudaStream_t stream);
+  // One send and one receive of raw bytes in a single NCCL group (either may be empty).
+  void sendrecv(const void* send, size_t send_bytes, int to, void* recv, size_t recv_bytes,
+                int from, cudaStream_t stream);
+  // Fixed-size alltoall of device buffers.
+  void alltoall(const void* send, void* recv, size_t bytes_per_pair, cudaStream_t stream);
+  // Poll the communicator for an asynchronous error; throws comm_error.
+  void check_async_error();
+};
+
+namespace wgb {
+
+void nccl_get_unique_id(wholegraph_unique_id_t* id);
+wholegraph_comm_* create_comm(const wholegraph_unique_id_t& id, int rank, int size);
+wholegraph_comm_* split_comm(wholegraph_comm_* comm, int color, int key);
+void destroy_comm(wholegraph_comm_* comm);
+void destroy_all_comms();
+
+}  // namespace wgb

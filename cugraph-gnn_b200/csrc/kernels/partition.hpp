@@ -1,0 +1,28 @@
+// Host interface of the stable partition-by-owner kernels.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+namespace wgb {
+
+constexpr int kMaxPartitionRanks = 64;
+
+// Bytes of device scratch partition_by_owner needs for a list of n ids.
+size_t partition_workspace_bytes(int64_t n, int world);
+
+// Group the ids of a request list by owning rank, keeping list order inside each group.
+//   ids          : n row ids (int32 or int64), device memory
+//   first_row    : HOST array of world + 1 first rows per rank (first_row[world] = table rows)
+//   sorted_ids   : out, n int64; group of rank r occupies [starts[r], starts[r] + counts[r])
+//   positions    : out, n int64; list position each sorted id came from
+//   counts/starts: out, world int64 each, DEVICE memory
+// Ids that are negative or >= first_row[world] belong to no group and are not written; the
+// groups are packed at the front of the output arrays.  n must be below 2^31.
+void partition_by_owner(const void* ids, bool ids_are_64, int64_t n, const int64_t* first_row,
+                        int world, void* workspace, int64_t* sorted_ids, int64_t* positions,
+                        int64_t* counts, int64_t* starts, cudaStream_t stream);
+
+}  // namespace wgb

@@ -1,0 +1,241 @@
+// Row copy kernel for sm_100a: gather, scatter and permutation reorder with a fused element
+// cast.  One warp owns a tile of 32 list positions: it stages the 32 row ids (and output
+// positions) in shared memory with one coalesced load, then walks the tile with several rows
+// in flight per lane, every access a single vector of up to 16 bytes.
+//
+// Semantics follow the reference's gather_func_kernel / scatter_func_kernel
+// (cpp/src/wholegraph_tensor_ops/functions/gather_scatter_func.cuh:242-365, :508-587): a
+// negative row id skips the position, casts go through fp32 for fp16 / bf16
+// (type_caster, :150-197), integer casts truncate.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdint>
+
+#include "row_copy.hpp"
+
+namespace wgb {
+
+constexpr int kRowCopyWarps       = 8;                   // warps per CTA
+constexpr int kRowCopyThreads     = kRowCopyWarps * 32;  // threads per CTA
+constexpr int kRowCopyTile        = 32;                  // list positions per warp tile
+constexpr int kRowCopyRowsInFlight = 4;                  // independent rows per lane per pass
+
+struct row_copy_params {
+  const char* src;  // first element of row 0 (storage offset already applied)
+  char* dst;
+  int64_t src_stride_bytes;
+  int64_t dst_stride_bytes;
+  const void* indices;
+  const int64_t* positions;
+  int64_t count;
+  int vectors_per_row;  // ceil(dim / EPV)
+  int lanes_per_row;    // power of two, 1..32
+  int src_select;
+  int dst_select;
+  int indices_are_64;
+  // CHUNKED tables: the BY_INDEX side ignores src / dst and resolves rows through `chunks`;
+  // chunk_offset_bytes is that side's storage offset.
+  int64_t chunk_offset_bytes;
+  chunked_table chunks;
+};
+
+// ---- raw vectors of 1..16 bytes ---------------------------------------------------------
+template <int BYTES>
+struct raw_vec;
+template <>
+struct raw_vec<1> {
+  using type = unsigned char;
+};
+template <>
+struct raw_vec<2> {
+  using type = unsigned short;
+};
+template <>
+struct raw_vec<4> {
+  using type = unsigned int;
+};
+template <>
+struct raw_vec<8> {
+  using type = uint2;
+};
+template <>
+struct raw_vec<16> {
+  using type = uint4;
+};
+
+// Read-only, no reuse expected: non-coherent path.
+template <int BYTES>
+__device__ __forceinline__ typename raw_vec<BYTES>::type load_row_vector(const char* p)
+{
+  return __ldg(reinterpret_cast<const typename raw_vec<BYTES>::type*>(p));
+}
+template <int BYTES>
+__device__ __forceinline__ void store_row_vector(char* p, typename raw_vec<BYTES>::type v)
+{
+  *reinterpret_cast<typename raw_vec<BYTES>::type*>(p) = v;
+}
+
+// ---- element conversion ----------------------------------------------------------------------
+template <typename T>
+struct wide_of {
+  using type = T;
+};
+template <>
+struct wide_of<__half> {
+  using type = float;
+};
+template <>
+struct wide_of<__nv_bfloat16> {
+  using type = float;
+};
+
+template <typename From, typename To>
+__device__ __forceinline__ To convert_element(From x)
+{
+  using wf = typename wide_of<From>::type;
+  using wt = typename wide_of<To>::type;
+  wf a     = static_cast<wf>(x);  // fp16 / bf16 widen to fp32 exactly
+  wt b     = static_cast<wt>(a);  // fp64 -> fp32 rounds to nearest; integers truncate
+  return static_cast<To>(b);      // fp32 -> fp16 / bf16 rounds to nearest even
+}
+
+template <typename From, typename To, int EPV>
+struct vector_cast {
+  using in_raw  = typename raw_vec<sizeof(From) * EPV>::type;
+  using out_raw = typename raw_vec<sizeof(To) * EPV>::type;
+  static __device__ __forceinline__ out_raw apply(in_raw v)
+  {
+    union {
+      in_raw raw;
+      From e[EPV];
+    } a;
+    union {
+      out_raw raw;
+      To e[EPV];
+    } b;
+    a.raw = v;
+#pragma unroll
+    for (int i = 0; i < EPV; i++) b.e[i] = convert_element<From, To>(a.e[i]);
+    return b.raw;
+  }
+};
+
+__device__ __forceinline__ const char* chunked_row(const chunked_table& t, int64_t row,
+                                                   int64_t stride_bytes, int64_t offset_bytes)
+{
+  int r = t.ranks - 1;
+  while (r > 0 && t.first_row[r] > row) r--;
+  return static_cast<const char*>(t.base[r]) + (row - t.first_row[r]) * stride_bytes + offset_bytes;
+}
+
+// IN_BYTES / OUT_BYTES: bytes per vector on each side.  CAST::apply converts one vector.
+template <int IN_BYTES, int OUT_BYTES, typename CAST, bool CHUNKED>
+__global__ void __launch_bounds__(kRowCopyThreads)
+  row_copy_kernel(const row_copy_params p)
+{
+  __shared__ int64_t s_index[kRowCopyWarps][kRowCopyTile];
+  __shared__ int64_t s_position[kRowCopyWarps][kRowCopyTile];
+
+  const int lane          = threadIdx.x & 31;
+  const int warp          = threadIdx.x >> 5;
+  const int lpr           = p.lanes_per_row;
+  const int sub           = lane / lpr;       // which row of a pass this lane works on
+  const int col0          = lane % lpr;       // first vector of the row this lane moves
+  const int rows_per_pass = 32 / lpr;
+  const bool need_index   = p.src_select == ROW_BY_INDEX || p.dst_select == ROW_BY_INDEX;
+  const bool need_pos     = p.src_select == ROW_BY_POSITION || p.dst_select == ROW_BY_POSITION;
+
+  const int64_t tiles       = (p.count + kRowCopyTile - 1) / kRowCopyTile;
+  const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * kRowCopyWarps + warp;
+  const int64_t warp_stride = static_cast<int64_t>(gridDim.x) * kRowCopyWarps;
+
+  for (int64_t tile = warp_global; tile < tiles; tile += warp_stride) {
+    const int64_t base = tile * kRowCopyTile;
+    {
+      const int64_t i = base + lane;
+      int64_t id      = -1;  // positions past the end behave like skipped rows
+      int64_t pos     = 0;
+      if (i < p.count) {
+        id = 0;
+        if (need_index)
+          id = p.indices_are_64 ? __ldg(static_cast<const int64_t*>(p.indices) + i)
+                                : static_cast<int64_t>(__ldg(static_cast<const int*>(p.indices) + i));
+        if (need_pos) pos = __ldg(p.positions + i);
+      }
+      s_index[warp][lane]    = id;
+      s_position[warp][lane] = pos;
+    }
+    __syncwarp();
+
+    for (int r0 = 0; r0 < kRowCopyTile; r0 += rows_per_pass * kRowCopyRowsInFlight) {
+      const char* src_row[kRowCopyRowsInFlight];
+      char* dst_row[kRowCopyRowsInFlight];
+      bool live[kRowCopyRowsInFlight];
+#pragma unroll
+      for (int k = 0; k < kRowCopyRowsInFlight; k++) {
+        const int r = r0 + k * rows_per_pass + sub;
+        live[k]     = false;
+        if (r < kRowCopyTile) {
+          const int64_t id  = s_index[warp][r];
+          const int64_t pos = s_position[warp][r];
+          const int64_t i   = base + r;
+          live[k]           = id >= 0;
+          const int64_t srow =
+            p.src_select == ROW_BY_INDEX ? id : (p.src_select == ROW_BY_POSITION ? pos : i);
+          const int64_t drow =
+            p.dst_select == ROW_BY_INDEX ? id : (p.dst_select == ROW_BY_POSITION ? pos : i);
+          if (CHUNKED && live[k]) {
+            if (p.src_select == ROW_BY_INDEX) {
+              src_row[k] = chunked_row(p.chunks, srow, p.src_stride_bytes, p.chunk_offset_bytes);
+              dst_row[k] = p.dst + drow * p.dst_stride_bytes;
+            } else {
+              src_row[k] = p.src + srow * p.src_stride_bytes;
+              dst_row[k] = const_cast<char*>(
+                chunked_row(p.chunks, drow, p.dst_stride_bytes, p.chunk_offset_bytes));
+            }
+          } else {
+            src_row[k] = p.src + srow * p.src_stride_bytes;
+            dst_row[k] = p.dst + drow * p.dst_stride_bytes;
+          }
+        }
+      }
+      for (int c = col0; c < p.vectors_per_row; c += lpr) {
+        typename raw_vec<IN_BYTES>::type v[kRowCopyRowsInFlight];
+#pragma unroll
+        for (int k = 0; k < kRowCopyRowsInFlight; k++)
+          if (live[k]) v[k] = load_row_vector<IN_BYTES>(src_row[k] + static_cast<int64_t>(c) * IN_BYTES);
+#pragma unroll
+        for (int k = 0; k < kRowCopyRowsInFlight; k++)
+          if (live[k])
+            store_row_vector<OUT_BYTES>(dst_row[k] + static_cast<int64_t>(c) * OUT_BYTES,
+                                        CAST::apply(v[k]));
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// Identity "cast" for same-type copies.
+template <int BYTES>
+struct raw_copy {
+  static __device__ __forceinline__ typename raw_vec<BYTES>::type apply(
+    typename raw_vec<BYTES>::type v)
+  {
+    return v;
+  }
+};
+
+using row_copy_kernel_fn = void (*)(const row_copy_params);
+
+// Kernel for a (from, to, elements-per-vector) triple, or nullptr when the vector would
+// exceed 16 bytes.  Defined in the per-family translation units.
+row_copy_kernel_fn float_cast_kernel(wholegraph_dtype_t from, wholegraph_dtype_t to, int epv,
+                                     bool chunked);
+row_copy_kernel_fn int_cast_kernel(wholegraph_dtype_t from, wholegraph_dtype_t to, int epv,
+                                   bool chunked);
+row_copy_kernel_fn same_type_kernel(int vector_bytes, bool chunked);
+
+}  // namespace wgb

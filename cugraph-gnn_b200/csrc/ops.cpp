@@ -1,0 +1,461 @@
+// wholegraph_gather / wholegraph_scatter: argument checks, mapped (direct pointer) path and
+// the distributed (alltoallv) path.
+//
+// Reference behaviour: cpp/src/wholegraph_tensor_ops/gather_op.cpp:12-106, scatter_op.cpp:12-98,
+// gather_op_impl_nccl.cu:23-171, scatter_op_impl_nccl.cu:23-170.  The distributed path here is
+// a W-step pipeline: at step s a rank gathers the rows its s-th neighbour asked for while the
+// rows of step s-1 are in flight on a second stream, and one host synchronisation (to learn
+// the per-rank counts) replaces the reference's three.
+#include "ops.hpp"
+
+#include <algorithm>
+#include <memory>
+#include <vector>
+
+#include <wholegraph/wholegraph_tensor_op.h>
+
+#include "common.hpp"
+#include "env.hpp"
+#include "handle.hpp"
+#include "kernels/partition.hpp"
+#include "kernels/row_copy.hpp"
+#include "tensor.hpp"
+
+namespace wgb {
+
+// ---- exchange plan -------------------------------------------------------------------------
+
+exchange_plan::exchange_plan(wholegraph_env_func_t* env)
+  : workspace(env), sorted_ids_buf(env), positions_buf(env), recv_ids_buf(env), counts_dev(env),
+    counts_pin(env)
+{
+}
+
+void exchange_plan::build(const void* ids, bool ids_are_64, int64_t n,
+                          const std::vector<int64_t>& first_row, wholegraph_comm_* comm,
+                          cudaStream_t stream)
+{
+  world = comm->world_size;
+  me    = comm->world_rank;
+  count = n;
+  send_counts.assign(world, 0);
+  send_displs.assign(world, 0);
+  recv_counts.assign(world, 0);
+  recv_displs.assign(world, 0);
+
+  void* ws   = workspace.device_bytes(partition_workspace_bytes(n, world));
+  sorted_ids = static_cast<int64_t*>(sorted_ids_buf.device(n, WHOLEGRAPH_DT_INT64));
+  positions  = static_cast<int64_t*>(positions_buf.device(n, WHOLEGRAPH_DT_INT64));
+  // Device layout: [send counts | send starts | recv counts], world entries each.
+  int64_t* cdev = static_cast<int64_t*>(counts_dev.device(3 * world, WHOLEGRAPH_DT_INT64));
+  int64_t* cpin = static_cast<int64_t*>(counts_pin.pinned(3 * world, WHOLEGRAPH_DT_INT64));
+  partition_by_owner(ids, ids_are_64, n, first_row.data(), world, ws, sorted_ids, positions, cdev,
+                     cdev + world, stream);
+  comm->alltoall(cdev, cdev + 2 * world, sizeof(int64_t), stream);
+  WGB_CUDA_CHECK(cudaMemcpyAsync(cpin, cdev, sizeof(int64_t) * 3 * world, cudaMemcpyDeviceToHost,
+                                 stream));
+  WGB_CUDA_CHECK(cudaStreamSynchronize(stream));  // the one host sync of a distributed op
+  comm->check_async_error();
+  total_send = total_recv = 0;
+  for (int r = 0; r < world; r++) {
+    send_counts[r] = cpin[r];
+    send_displs[r] = cpin[world + r];
+    recv_counts[r] = cpin[2 * world + r];
+    recv_displs[r] = total_recv;
+    total_send += send_counts[r];
+    total_recv += recv_counts[r];
+  }
+  recv_ids = static_cast<int64_t*>(recv_ids_buf.device(total_recv, WHOLEGRAPH_DT_INT64));
+  comm->alltoallv(sorted_ids, send_counts.data(), send_displs.data(), recv_ids, recv_counts.data(),
+                  recv_displs.data(), sizeof(int64_t), stream);
+}
+
+std::vector<int64_t> entry_offsets_of(wholegraph_handle_* h, size_t entry_bytes)
+{
+  std::vector<int64_t> first(h->part_offsets.size());
+  for (size_t i = 0; i < first.size(); i++) {
+    WGB_EXPECTS(h->part_offsets[i] % entry_bytes == 0,
+                "shard offset %zu of rank %zu is not a multiple of the row size %zu",
+                h->part_offsets[i], i, entry_bytes);
+    first[i] = static_cast<int64_t>(h->part_offsets[i] / entry_bytes);
+  }
+  return first;
+}
+
+namespace {
+
+struct matrix_view {
+  void* ptr;  // element 0 of the storage (offset not applied)
+  wholegraph_matrix_description_t d;
+};
+
+// 1-D tensors are [N, 1] matrices (reference: gather_op.cpp:33-38, :53-58).
+bool as_matrix(wholegraph_tensor_t t, wholegraph_matrix_description_t* m)
+{
+  wholegraph_tensor_description_t d = *wholegraph_tensor_get_tensor_description(t);
+  if (d.dim != 1 && d.dim != 2) return false;
+  if (d.dim == 1 && !wholegraph_unsqueeze_tensor(&d, 1)) return false;
+  return wholegraph_convert_tensor_desc_to_matrix(m, &d);
+}
+
+void fill_chunks(chunked_table* c, wholegraph_handle_* h, size_t entry_bytes)
+{
+  int W = h->comm->world_size;
+  WGB_EXPECTS(W <= kMaxChunkedRanks, "CHUNKED memory supports up to %d ranks", kMaxChunkedRanks);
+  auto first = entry_offsets_of(h, entry_bytes);
+  c->ranks   = W;
+  for (int r = 0; r < W; r++) {
+    c->base[r]      = h->rank_ptrs[r];
+    c->first_row[r] = first[r];
+  }
+  c->first_row[W] = first[W];
+}
+
+// A pointer such that row `first_local_row` of the global numbering lands on local_ptr
+// (reference: gather_op_impl_nccl.cu:111-115).
+const void* fake_global_base(wholegraph_handle_* h)
+{
+  return static_cast<const char*>(h->local_ptr) - h->part_offsets[h->comm->world_rank];
+}
+
+struct table_side {
+  const void* base = nullptr;
+  chunked_table chunks;
+};
+
+// ---- distributed gather ----------------------------------------------------------------------
+void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_description_t& tab,
+                        const void* ids, bool ids_are_64, int64_t n, void* out,
+                        const wholegraph_matrix_description_t& od, wholegraph_env_func_t* env,
+                        cudaStream_t stream, int sms)
+{
+  WGB_EXPECTS(tab.storage_offset >= 0 && tab.storage_offset + tab.sizes[1] <= tab.stride,
+              "distributed gather needs storage_offset + dim <= stride");
+  auto* comm           = h->comm;
+  const int W          = comm->world_size;
+  const int me         = comm->world_rank;
+  const size_t es_tab  = wholegraph_dtype_get_element_size(tab.dtype);
+  const size_t es_out  = wholegraph_dtype_get_element_size(od.dtype);
+  const int64_t dim    = tab.sizes[1];
+  const size_t row_b   = static_cast<size_t>(dim) * es_out;
+  auto first_row       = entry_offsets_of(h, es_tab * static_cast<size_t>(tab.stride));
+  const void* fake_tab = fake_global_base(h);
+
+  row_copy_args g;  // local shard -> rows, by index
+  g.src = fake_tab, g.src_dt = tab.dtype, g.src_stride = tab.stride, g.src_offset = tab.storage_offset;
+  g.src_select = ROW_BY_INDEX;
+  g.dst_dt = od.dtype, g.dim = dim, g.indices_are_64 = true, g.sm_hint = sms;
+
+  if (W == 1) {
+    g.dst = out, g.dst_stride = od.stride, g.dst_offset = od.storage_offset;
+    g.indices = ids, g.indices_are_64 = ids_are_64, g.count = n;
+    launch_row_copy(g, stream);
+    return;
+  }
+
+  exchange_plan plan(env);
+  plan.build(ids, ids_are_64, n, first_row, comm, stream);
+
+  temp_buffer serve_buf(env), recv_buf(env);
+  char* serve = static_cast<char*>(serve_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
+  char* recv  = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
+
+  // Step 0: rows this rank owns go straight from the shard to their final output rows.
+  {
+    row_copy_args a = g;
+    a.dst = out, a.dst_stride = od.stride, a.dst_offset = od.storage_offset;
+    a.dst_select = ROW_BY_POSITION;
+    a.indices    = plan.sorted_ids + plan.send_displs[me];
+    a.positions  = plan.positions + plan.send_displs[me];
+    a.count      = plan.send_counts[me];
+    launch_row_copy(a, stream);
+  }
+  row_copy_args reorder;  // received rows -> output rows, by position
+  reorder.src_dt = od.dtype, reorder.src_stride = dim, reorder.src_select = ROW_SEQUENTIAL;
+  reorder.dst = out, reorder.dst_dt = od.dtype, reorder.dst_stride = od.stride;
+  reorder.dst_offset = od.storage_offset, reorder.dst_select = ROW_BY_POSITION;
+  reorder.dim = dim, reorder.sm_hint = sms;
+
+  cudaStream_t xs = comm->xchg_stream;
+  auto reorder_step = [&](int s) {
+    const int from = (me - s + W) % W;
+    WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(2 * s + 1), 0));
+    row_copy_args r = reorder;
+    r.src           = recv + plan.send_displs[from] * row_b;
+    r.positions     = plan.positions + plan.send_displs[from];
+    r.count         = plan.send_counts[from];
+    launch_row_copy(r, stream);
+  };
+  for (int s = 1; s < W; s++) {
+    const int to   = (me + s) % W;      // whose requests are served now
+    const int from = (me - s + W) % W;  // who serves this rank's requests now
+    row_copy_args a = g;
+    a.dst = serve + plan.recv_displs[to] * row_b, a.dst_stride = dim, a.dst_offset = 0;
+    a.dst_select = ROW_SEQUENTIAL;
+    a.indices    = plan.recv_ids + plan.recv_displs[to];
+    a.count      = plan.recv_counts[to];
+    launch_row_copy(a, stream);
+    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s), stream));
+    WGB_CUDA_CHECK(cudaStreamWaitEvent(xs, comm->event(2 * s), 0));
+    comm->sendrecv(serve + plan.recv_displs[to] * row_b, plan.recv_counts[to] * row_b, to,
+                   recv + plan.send_displs[from] * row_b, plan.send_counts[from] * row_b, from, xs);
+    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s + 1), xs));
+    if (s > 1) reorder_step(s - 1);  // overlaps with the exchange just enqueued
+  }
+  reorder_step(W - 1);
+}
+
+// ---- distributed scatter ---------------------------------------------------------------------
+void scatter_distributed(const void* in, const wholegraph_matrix_description_t& id_,
+                         const void* ids, bool ids_are_64, int64_t n, wholegraph_handle_* h,
+                         const wholegraph_matrix_description_t& tab, wholegraph_env_func_t* env,
+                         cudaStream_t stream, int sms)
+{
+  WGB_EXPECTS(tab.storage_offset >= 0 && tab.storage_offset + tab.sizes[1] <= tab.stride,
+              "distributed scatter needs storage_offset + dim <= stride");
+  auto* comm          = h->comm;
+  const int W         = comm->world_size;
+  const int me        = comm->world_rank;
+  const size_t es_tab = wholegraph_dtype_get_element_size(tab.dtype);
+  const size_t es_in  = wholegraph_dtype_get_element_size(id_.dtype);
+  const int64_t dim   = tab.sizes[1];
+  const size_t row_b  = static_cast<size_t>(dim) * es_in;  // rows travel in the input dtype
+  auto first_row      = entry_offsets_of(h, es_tab * static_cast<size_t>(tab.stride));
+  void* fake_tab      = const_cast<void*>(fake_global_base(h));
+
+  row_copy_args put;  // rows -> local shard, by index (cast to the table dtype happens here)
+  put.src_dt = id_.dtype, put.dst = fake_tab, put.dst_dt = tab.dtype, put.dst_stride = tab.stride;
+  put.dst_offset = tab.storage_offset, put.dst_select = ROW_BY_INDEX;
+  put.dim = dim, put.indices_are_64 = true, put.sm_hint = sms;
+
+  if (W == 1) {
+    put.src = in, put.src_stride = id_.stride, put.src_offset = id_.storage_offset;
+    put.indices = ids, put.indices_are_64 = ids_are_64, put.count = n;
+    launch_row_copy(put, stream);
+    WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
+    return;
+  }
+
+  exchange_plan plan(env);
+  plan.build(ids, ids_are_64, n, first_row, comm, stream);
+  temp_buffer send_buf(env), recv_buf(env);
+  char* send = static_cast<char*>(send_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
+  char* recv = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
+
+  {  // step 0: this rank's own rows
+    row_copy_args a = put;
+    a.src = in, a.src_stride = id_.stride, a.src_offset = id_.storage_offset;
+    a.src_select = ROW_BY_POSITION;
+    a.indices    = plan.sorted_ids + plan.send_displs[me];
+    a.positions  = plan.positions + plan.send_displs[me];
+    a.count      = plan.send_counts[me];
+    launch_row_copy(a, stream);
+  }
+  cudaStream_t xs = comm->xchg_stream;
+  auto store_step = [&](int s) {
+    const int from = (me - s + W) % W;
+    WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(2 * s + 1), 0));
+    row_copy_args a = put;
+    a.src = recv + plan.recv_displs[from] * row_b, a.src_stride = dim, a.src_offset = 0;
+    a.src_select = ROW_SEQUENTIAL;
+    a.indices    = plan.recv_ids + plan.recv_displs[from];
+    a.count      = plan.recv_counts[from];
+    launch_row_copy(a, stream);
+  };
+  for (int s = 1; s < W; s++) {
+    const int to   = (me + s) % W;
+    const int from = (me - s + W) % W;
+    row_copy_args pack;  // input rows of this peer, in send order
+    pack.src = in, pack.src_dt = id_.dtype, pack.src_stride = id_.stride;
+    pack.src_offset = id_.storage_offset, pack.src_select = ROW_BY_POSITION;
+    pack.dst = send + plan.send_displs[to] * row_b, pack.dst_dt = id_.dtype, pack.dst_stride = dim;
+    pack.dim = dim, pack.sm_hint = sms;
+    pack.positions = plan.positions + plan.send_displs[to];
+    pack.count     = plan.send_counts[to];
+    launch_row_copy(pack, stream);
+    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s), stream));
+    WGB_CUDA_CHECK(cudaStreamWaitEvent(xs, comm->event(2 * s), 0));
+    comm->sendrecv(send + plan.send_displs[to] * row_b, plan.send_counts[to] * row_b, to,
+                   recv + plan.recv_displs[from] * row_b, plan.recv_counts[from] * row_b, from, xs);
+    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s + 1), xs));
+    if (s > 1) store_step(s - 1);
+  }
+  store_step(W - 1);
+  // The reference returns with the local shard updated (scatter_op_impl_nccl.cu:157).
+  WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
+}
+
+}  // namespace
+}  // namespace wgb
+
+using namespace wgb;
+
+extern "C" {
+
+wholegraph_error_code_t wholegraph_gather(wholegraph_tensor_t table,
+                                            wholegraph_tensor_t indices_tensor,
+                                            wholegraph_tensor_t output_tensor,
+                                            wholegraph_env_func_t* p_env_fns,
+                                            void* stream_ptr,
+                                            int gather_sms)
+{
+  if (table == nullptr || indices_tensor == nullptr || output_tensor == nullptr)
+    return WHOLEGRAPH_INVALID_INPUT;
+  WGB_API_BEGIN
+  auto stream = static_cast<cudaStream_t>(stream_ptr);
+  wholegraph_matrix_description_t tab, od;
+  const int table_dim = wholegraph_tensor_get_tensor_description(table)->dim;
+  if (table_dim != 1 && table_dim != 2) {
+    WGB_ERROR("wholegraph_gather: the table must be 1-D or 2-D");
+    return WHOLEGRAPH_INVALID_INPUT;
+  }
+  if (!as_matrix(table, &tab)) return WHOLEGRAPH_LOGIC_ERROR;
+  auto* idx_td = wholegraph_tensor_get_tensor_description(indices_tensor);
+  if (idx_td->dim != 1) {
+    WGB_ERROR("wholegraph_gather: indices must be 1-D");
+    return WHOLEGRAPH_INVALID_INPUT;
+  }
+  if (wholegraph_tensor_get_tensor_description(output_tensor)->dim != table_dim) {
+    WGB_ERROR("wholegraph_gather: output must have as many dimensions as the table");
+    return WHOLEGRAPH_INVALID_INPUT;
+  }
+  wholegraph_array_description_t idx;
+  if (!wholegraph_convert_tensor_desc_to_array(&idx, idx_td)) return WHOLEGRAPH_INVALID_INPUT;
+  if (!as_matrix(output_tensor, &od)) return WHOLEGRAPH_INVALID_INPUT;
+  void* ids = wholegraph_tensor_get_data_pointer(indices_tensor);  // offset applied
+  void* out = wholegraph_tensor_get_data_pointer(output_tensor);
+  if (out != nullptr)
+    out = static_cast<char*>(out) - od.storage_offset * wholegraph_dtype_get_element_size(od.dtype);
+  // Anything that is not int32 is read as int64 (reference: gather_func.cu:82-86).
+  const bool ids_are_64 = idx.dtype != WHOLEGRAPH_DT_INT;
+  const bool f_ok = wholegraph_dtype_is_floating_number(tab.dtype) &&
+                    wholegraph_dtype_is_floating_number(od.dtype);
+  const bool i_ok = wholegraph_dtype_is_integer_number(tab.dtype) &&
+                    wholegraph_dtype_is_integer_number(od.dtype);
+  if (!f_ok && !i_ok) {
+    WGB_ERROR("wholegraph_gather: table dtype %d and output dtype %d do not mix", (int)tab.dtype,
+              (int)od.dtype);
+    return WHOLEGRAPH_LOGIC_ERROR;
+  }
+  if (od.sizes[0] != idx.size) {
+    WGB_ERROR("wholegraph_gather: output has %ld rows for %ld indices", (long)od.sizes[0],
+              (long)idx.size);
+    return WHOLEGRAPH_LOGIC_ERROR;
+  }
+  if (od.sizes[1] != tab.sizes[1]) {
+    WGB_ERROR("wholegraph_gather: output rows have %ld elements, table rows %ld", (long)od.sizes[1],
+              (long)tab.sizes[1]);
+    return WHOLEGRAPH_LOGIC_ERROR;
+  }
+  if (idx.size == 0 || tab.sizes[1] == 0) return WHOLEGRAPH_SUCCESS;
+  if (ids == nullptr || out == nullptr) return WHOLEGRAPH_INVALID_INPUT;
+
+  wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(table);
+  if (h != nullptr && h->type == WHOLEGRAPH_MT_DISTRIBUTED) {
+    gather_distributed(h, tab, ids, ids_are_64, idx.size, out, od, p_env_fns, stream, gather_sms);
+    return WHOLEGRAPH_SUCCESS;
+  }
+  row_copy_args a;
+  a.src_dt = tab.dtype, a.src_stride = tab.stride, a.src_offset = tab.storage_offset;
+  a.src_select = ROW_BY_INDEX;
+  a.dst = out, a.dst_dt = od.dtype, a.dst_stride = od.stride, a.dst_offset = od.storage_offset;
+  a.count = idx.size, a.dim = tab.sizes[1], a.indices = ids, a.indices_are_64 = ids_are_64;
+  a.sm_hint = gather_sms;
+  if (h != nullptr && h->type == WHOLEGRAPH_MT_CHUNKED) {
+    fill_chunks(&a.chunks, h,
+                wholegraph_dtype_get_element_size(tab.dtype) *
+                  static_cast<size_t>(table->root->desc.dim == 2 ? table->root->desc.strides[0] : 1));
+  } else {
+    wholegraph_gref_t gref;
+    WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_tensor_get_global_reference(table, &gref));
+    a.src = gref.pointer;
+  }
+  launch_row_copy(a, stream);
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_gather")
+}
+
+wholegraph_error_code_t wholegraph_scatter(wholegraph_tensor_t input_tensor,
+                                             wholegraph_tensor_t indices_tensor,
+                                             wholegraph_tensor_t table,
+                                             wholegraph_env_func_t* p_env_fns,
+                                             void* stream_ptr,
+                                             int scatter_sms)
+{
+  if (table == nullptr || indices_tensor == nullptr || input_tensor == nullptr)
+    return WHOLEGRAPH_INVALID_INPUT;
+  WGB_API_BEGIN
+  auto stream = static_cast<cudaStream_t>(stream_ptr);
+  wholegraph_matrix_description_t tab, id_;
+  const int table_dim = wholegraph_tensor_get_tensor_description(table)->dim;
+  if (table_dim != 1 && table_dim != 2) {
+    WGB_ERROR("wholegraph_scatter: the table must be 1-D or 2-D");
+    return WHOLEGRAPH_INVALID_INPUT;
+  }
+  if (!as_matrix(table, &tab)) return WHOLEGRAPH_LOGIC_ERROR;
+  auto* idx_td = wholegraph_tensor_get_tensor_description(indices_tensor);
+  if (idx_td->dim != 1) {
+    WGB_ERROR("wholegraph_scatter: indices must be 1-D");
+    return WHOLEGRAPH_INVALID_INPUT;
+  }
+  if (wholegraph_tensor_get_tensor_description(input_tensor)->dim != table_dim) {
+    WGB_ERROR("wholegraph_scatter: input must have as many dimensions as the table");
+    return WHOLEGRAPH_INVALID_INPUT;
+  }
+  wholegraph_array_description_t idx;
+  if (!wholegraph_convert_tensor_desc_to_array(&idx, idx_td)) return WHOLEGRAPH_INVALID_INPUT;
+  if (!as_matrix(input_tensor, &id_)) return WHOLEGRAPH_INVALID_INPUT;
+  void* ids      = wholegraph_tensor_get_data_pointer(indices_tensor);
+  const void* in = wholegraph_tensor_get_data_pointer(input_tensor);
+  if (in != nullptr)
+    in = static_cast<const char*>(in) -
+         id_.storage_offset * wholegraph_dtype_get_element_size(id_.dtype);
+  const bool ids_are_64 = idx.dtype != WHOLEGRAPH_DT_INT;
+  const bool f_ok = wholegraph_dtype_is_floating_number(tab.dtype) &&
+                    wholegraph_dtype_is_floating_number(id_.dtype);
+  const bool i_ok = wholegraph_dtype_is_integer_number(tab.dtype) &&
+                    wholegraph_dtype_is_integer_number(id_.dtype);
+  if (!f_ok && !i_ok) {
+    WGB_ERROR("wholegraph_scatter: table dtype %d and input dtype %d do not mix", (int)tab.dtype,
+              (int)id_.dtype);
+    return WHOLEGRAPH_LOGIC_ERROR;
+  }
+  if (id_.sizes[0] != idx.size) {
+    WGB_ERROR("wholegraph_scatter: input has %ld rows for %ld indices", (long)id_.sizes[0],
+              (long)idx.size);
+    return WHOLEGRAPH_LOGIC_ERROR;
+  }
+  if (id_.sizes[1] != tab.sizes[1]) {
+    WGB_ERROR("wholegraph_scatter: input rows have %ld elements, table rows %ld",
+              (long)id_.sizes[1], (long)tab.sizes[1]);
+    return WHOLEGRAPH_LOGIC_ERROR;
+  }
+  if (idx.size == 0 || tab.sizes[1] == 0) return WHOLEGRAPH_SUCCESS;
+  if (ids == nullptr || in == nullptr) return WHOLEGRAPH_INVALID_INPUT;
+
+  wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(table);
+  if (h != nullptr && h->type == WHOLEGRAPH_MT_DISTRIBUTED) {
+    scatter_distributed(in, id_, ids, ids_are_64, idx.size, h, tab, p_env_fns, stream, scatter_sms);
+    return WHOLEGRAPH_SUCCESS;
+  }
+  row_copy_args a;
+  a.src = in, a.src_dt = id_.dtype, a.src_stride = id_.stride, a.src_offset = id_.storage_offset;
+  a.dst_dt = tab.dtype, a.dst_stride = tab.stride, a.dst_offset = tab.storage_offset;
+  a.dst_select = ROW_BY_INDEX;
+  a.count = idx.size, a.dim = tab.sizes[1], a.indices = ids, a.indices_are_64 = ids_are_64;
+  a.sm_hint = scatter_sms;
+  if (h != nullptr && h->type == WHOLEGRAPH_MT_CHUNKED) {
+    fill_chunks(&a.chunks, h,
+                wholegraph_dtype_get_element_size(tab.dtype) *
+                  static_cast<size_t>(table->root->desc.dim == 2 ? table->root->desc.strides[0] : 1));
+  } else {
+    wholegraph_gref_t gref;
+    WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_tensor_get_global_reference(table, &gref));
+    a.dst = gref.pointer;
+  }
+  launch_row_copy(a, stream);
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_scatter")
+}
+
+}  // extern "C"

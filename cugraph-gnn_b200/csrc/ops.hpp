@@ -1,0 +1,43 @@
+// Shared pieces of the distributed ops: the id exchange plan.
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+#include <vector>
+
+#include "comm.hpp"
+#include "env.hpp"
+#include "handle.hpp"
+
+namespace wgb {
+
+// Result of routing one rank's request list to the owners of the rows
+// (role of the reference's bucket_and_exchange_ids_func,
+// cpp/src/wholegraph_tensor_ops/functions/exchange_ids_nccl_func.cu:146-215).
+struct exchange_plan {
+  explicit exchange_plan(wholegraph_env_func_t* env);
+
+  // Partition `ids` by owner, exchange the per-rank counts (one host synchronisation of
+  // `stream`) and then the ids themselves (asynchronous on `stream`).
+  void build(const void* ids, bool ids_are_64, int64_t n, const std::vector<int64_t>& first_row,
+             wholegraph_comm_* comm, cudaStream_t stream);
+
+  int world = 1, me = 0;
+  int64_t count = 0;  // length of the request list
+  // Host copies, in rows.  send_* describe this rank's requests grouped by owner (positions in
+  // sorted_ids / positions); recv_* describe the requests other ranks sent here (in recv_ids).
+  std::vector<int64_t> send_counts, send_displs, recv_counts, recv_displs;
+  int64_t total_send = 0, total_recv = 0;
+  int64_t* sorted_ids = nullptr;  // device, global row ids grouped by owner
+  int64_t* positions  = nullptr;  // device, list position of each sorted id
+  int64_t* recv_ids   = nullptr;  // device, global row ids this rank must serve
+
+ private:
+  temp_buffer workspace, sorted_ids_buf, positions_buf, recv_ids_buf, counts_dev, counts_pin;
+};
+
+// First row of every rank's shard (world + 1 entries) for rows of `entry_bytes` bytes.
+std::vector<int64_t> entry_offsets_of(wholegraph_handle_* h, size_t entry_bytes);
+
+}  // namespace wgb
