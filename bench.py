@@ -1,0 +1,382 @@
+"""Benchmark of the WholeGraph gather hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One step = one wholegraph_gather call over one batch of synthetic, seeded indices.
+  N = 1 : "C2"  table 10,000,000 x 128 fp32 (CONTINUOUS/DEVICE), 1,048,576 int64 ids uniform with
+          replacement, output cast to fp16.
+  N > 1 : "C3"  table 100,000,000 x 128 fp16 row-sharded CONTINUOUS/DEVICE (direct NVLink loads),
+          1,048,576 int64 Zipf(1.1) ids per rank over a seeded permutation, fp16 output, every
+          rank gathering at once (launch with torchrun, one rank per GPU).
+Rank 0 prints one JSON line: `value` is gathered (output) GB/s summed over ranks with inputs
+resident in HBM; `e2e` is the same metric with pinned-host index and output buffers copied
+inside the timed region; `roofline` relates the copy kernel to the measured HBM (N = 1) or
+NVLink (N > 1) peak; `cpu_baseline` times the CPU oracle on the host cores beside it.
+`--impl reference` times only that CPU restatement (the reference has no CPU gather of its own).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROW_DIM = 128
+IDS_PER_RANK = 1_048_576
+HBM_FALLBACK_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+NVLINK_PEER_GBS = 770.0     # measured peer copy, per direction per GPU
+INDEX_BATCHES = 4           # distinct index batches cycled through the steps
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "c2", "c3"])
+    ap.add_argument("--rows", type=int, default=0, help="override the table rows (profiling on a small case)")
+    ap.add_argument("--ids", type=int, default=0, help="override the ids per rank")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val == "Active":
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+        return out
+
+
+def zipf_ids(torch, n, rows, alpha, perm, gen):
+    """Bounded power-law ranks by inverse CDF, mapped through a permutation of the row ids."""
+    u = torch.rand(n, generator=gen, device="cuda", dtype=torch.float64)
+    e = 1.0 - alpha
+    rank = torch.floor(((float(rows) ** e - 1.0) * u + 1.0) ** (1.0 / e)).to(torch.int64)
+    rank = rank.clamp_(1, rows) - 1
+    return perm[rank] if perm is not None else rank
+
+
+def cpu_oracle_gather_rate(table_np, idx_np, out_dt, threads, budget_s=12.0, min_reps=2):
+    """Output GB/s of the CPU oracle's gather on the host cores."""
+    from oracle import oracle as orc
+    import numpy as np
+    n, dim = idx_np.shape[0], table_np.shape[1]
+    out = np.zeros((n, dim), dtype=orc.np_dtype(out_dt))
+    orc.gather(table_np, idx_np, out_dt=out_dt, out=out, threads=threads)  # warm-up
+    times, t_begin = [], time.perf_counter()
+    while len(times) < min_reps or (time.perf_counter() - t_begin < budget_s and len(times) < 40):
+        t0 = time.perf_counter()
+        orc.gather(table_np, idx_np, out_dt=out_dt, out=out, threads=threads)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return n * dim * out.itemsize / best / 1e9, best, len(times)
+
+
+def run_reference_arm(args):
+    """CPU restatement of the reference's gather on the host cores; rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import numpy as np
+    from oracle import oracle as orc
+    multi = args.gpus > 1
+    threads = os.cpu_count() or 1
+    ids = args.ids or IDS_PER_RANK
+    # Bounded sample: the table is cut to what the host can fill in seconds; the request list
+    # keeps its full length and its distribution.
+    rows = args.rows or 2_000_000
+    rng = np.random.default_rng(0)
+    if multi:
+        table = rng.uniform(-1, 1, size=(rows, ROW_DIM)).astype(np.float16)
+        e = 1.0 - 1.1
+        u = np.random.default_rng(100).random(ids)
+        rank = np.clip(np.floor(((rows ** e - 1.0) * u + 1.0) ** (1.0 / e)).astype(np.int64), 1, rows) - 1
+        idx = np.random.default_rng(7).permutation(rows)[rank]
+        out_dt, workload = orc.DT_HALF, "C3 sample"
+    else:
+        table = rng.uniform(-1, 1, size=(rows, ROW_DIM)).astype(np.float32)
+        idx = np.random.default_rng(1).integers(0, rows, size=ids, dtype=np.int64)
+        out_dt, workload = orc.DT_HALF, "C2 sample"
+    out = np.zeros((ids, ROW_DIM), dtype=orc.np_dtype(out_dt))
+    for _ in range(max(args.warmup, 1)):
+        orc.gather(table, idx, out_dt=out_dt, out=out, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.gather(table, idx, out_dt=out_dt, out=out, threads=threads)
+    dt = time.perf_counter() - t0
+    value = args.steps * ids * ROW_DIM * out.itemsize / dt / 1e9
+    sample = f"{workload}: table cut to {rows} x {ROW_DIM} rows on the host, {ids} ids per step, {threads} threads"
+    line = {
+        "impl": "reference", "metric": "gathered embedding GB/s", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32->f16" if not multi else "f16", "data": "synthetic",
+        "config": {"workload": workload, "note": "CPU restatement of the reference kernels (the reference has no CPU gather)"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+
+    pkg = load_package()
+    wgb = pkg.binding
+    from cugraph_gnn_b200 import torch_utils as tu
+    wgb.load_library()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("launch multi-GPU runs with torch.distributed.run, one rank per GPU")
+    torch.cuda.set_device(local_rank)
+    wgb.init(0, 2)
+    multi = world > 1
+    workload = args.workload if args.workload != "auto" else ("c3" if multi else "c2")
+
+    comm = None
+    if multi:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        raw = wgb.unique_id_to_bytes(wgb.create_unique_id()) if rank == 0 else bytes(128)
+        buf = torch.frombuffer(bytearray(raw), dtype=torch.uint8).cuda()
+        dist.broadcast(buf, 0)
+        uid = wgb.unique_id_from_bytes(buf.cpu().numpy().tobytes())
+        comm = wgb.create_communicator(uid, rank, world)
+    else:
+        comm = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+
+    n_ids = args.ids or IDS_PER_RANK
+    if workload == "c2":
+        rows = args.rows or 10_000_000
+        tab_dtype, out_dtype, tab_wg = torch.float32, torch.float16, wgb.WholeGraphDataType.DtFloat
+        name = f"C2: {rows} x {ROW_DIM} fp32 CONTINUOUS/DEVICE table, {n_ids} int64 ids uniform with replacement, gather with cast to fp16"
+    else:
+        rows = args.rows or 100_000_000
+        tab_dtype, out_dtype, tab_wg = torch.float16, torch.float16, wgb.WholeGraphDataType.DtHalf
+        name = (f"C3: {rows} x {ROW_DIM} fp16 table row-sharded CONTINUOUS/DEVICE over {world} GPUs, "
+                f"{n_ids} int64 Zipf(1.1) ids per rank over a seeded permutation, fp16 output")
+    es_tab = torch.empty((), dtype=tab_dtype).element_size()
+    es_out = torch.empty((), dtype=out_dtype).element_size()
+
+    desc = wgb.make_description([rows, ROW_DIM], tab_wg)
+    table = wgb.create_wholegraph_tensor(desc, comm, wgb.WholeGraphMemoryType.MtContinuous,
+                                         wgb.WholeGraphMemoryLocation.MlDevice)
+    shard = tu.local_shard_as_torch(table)
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    chunk = 4_000_000
+    for s in range(0, shard.shape[0], chunk):  # fill in pieces: uniform_ on fp16 makes fp32 temporaries
+        shard[s:s + chunk].uniform_(-1, 1, generator=gen)
+
+    batches = []
+    if workload == "c2":
+        for b in range(INDEX_BATCHES):
+            g = torch.Generator(device="cuda").manual_seed(1 + b)
+            batches.append(torch.randint(0, rows, (n_ids,), generator=g, device="cuda", dtype=torch.int64))
+    else:
+        perm = torch.randperm(rows, generator=torch.Generator(device="cuda").manual_seed(7), device="cuda")
+        for b in range(INDEX_BATCHES):
+            g = torch.Generator(device="cuda").manual_seed(100 + rank + 1000 * b)
+            batches.append(zipf_ids(torch, n_ids, rows, 1.1, perm, g))
+        del perm
+        torch.cuda.empty_cache()
+    out = torch.empty((n_ids, ROW_DIM), dtype=out_dtype, device="cuda")
+    env = wgb.cached_env_fns()
+    wraps = [tu.wrap_torch_tensor(b) for b in batches]
+    wout = tu.wrap_torch_tensor(out)
+    stream = tu.current_stream_int()
+
+    def step(i):
+        wgb.wholegraph_gather_op(table, wraps[i % INDEX_BATCHES], wout, env, stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if multi:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if not multi:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing ------------------------------------------------------------
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = wgb.lib().wholegraph_b200_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    launches = wgb.lib().wholegraph_b200_kernel_launch_count() - launches0
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+    out_bytes = n_ids * ROW_DIM * es_out
+    value = world * out_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end: pinned host ids in, pinned host rows out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        h_idx = [b.cpu().pin_memory() for b in batches]
+        h_out = torch.empty((n_ids, ROW_DIM), dtype=out_dtype).pin_memory()
+        d_idx = torch.empty_like(batches[0])
+        w_didx = tu.wrap_torch_tensor(d_idx)
+
+        def e2e_step(i):
+            d_idx.copy_(h_idx[i % INDEX_BATCHES], non_blocking=True)
+            wgb.wholegraph_gather_op(table, w_didx, wout, env, stream)
+            h_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()  # the caller reads the rows on the host
+
+        for i in range(min(args.warmup, 3)):
+            e2e_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            e2e_step(i)
+        barrier()
+        e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / args.steps
+        e2e = {"value": world * out_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+               "h2d_bytes_per_step": n_ids * 8, "d2h_bytes_per_step": out_bytes,
+               "ms_per_step": e2e_ms}
+        wgb.destroy_wholegraph_tensor(w_didx)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- roofline of the copy kernel -------------------------------------------------------
+    algorithmic = n_ids * (ROW_DIM * es_tab + ROW_DIM * es_out + 8)   # row read + row write + id read
+    if multi:
+        ingress = n_ids * ROW_DIM * es_tab * (world - 1) / world
+        achieved = ingress / (ms_step * 1e-3) / 1e9
+        roofline = {"bound": "nvlink", "achieved": achieved, "peak": NVLINK_PEER_GBS, "unit": "GB/s",
+                    "frac": achieved / NVLINK_PEER_GBS, "traffic": None,
+                    "note": "NVLink ingress bytes per rank per launch ((W-1)/W of the row reads) over the "
+                            "measured 770 GB/s peer copy; uniform-owner estimate, of measured"}
+    else:
+        peak, how = measured_hbm_peak()
+        achieved = algorithmic / (ms_step * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                    "frac": achieved / peak, "traffic": None, "peak_source": how,
+                    "algorithmic_bytes_per_launch": algorithmic}
+
+    # ---- CPU oracle beside it (rank 0, N = 1 only) ----------------------------------------
+    cpu = None
+    if not multi and not args.no_cpu_baseline and rank == 0:
+        from oracle import oracle as orc
+        sample_rows = min(rows, 2_000_000)
+        table_np = shard[:sample_rows].cpu().numpy()
+        idx_np = (batches[0] % sample_rows).cpu().numpy()
+        threads = os.cpu_count() or 1
+        gbs, best, reps = cpu_oracle_gather_rate(table_np, idx_np, orc.DT_HALF, threads)
+        cpu = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": f"first {sample_rows} table rows on the host, {n_ids} ids, best of {reps} passes "
+                         f"({best * 1e3:.1f} ms) of the CPU oracle's gather with cast to fp16"}
+
+    if rank == 0:
+        line = {
+            "metric": "gathered embedding GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32->f16" if workload == "c2" else "f16", "data": "synthetic",
+            "config": {"workload": name, "l2": "table and output larger than L2; a different index batch each step",
+                       "memory_type": "CONTINUOUS/DEVICE", "ids_per_rank": n_ids, "rows": rows, "dim": ROW_DIM},
+            "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks,
+        }
+        if e2e is not None:
+            line["e2e"] = e2e
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+
+    for w in wraps + [wout]:
+        wgb.destroy_wholegraph_tensor(w)
+    barrier()
+    wgb.destroy_wholegraph_tensor(table)
+    wgb.destroy_communicator(comm)
+    if multi:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,345 @@
+"""ctypes binding of libwholegraph.so (the sm_100a build in this package).
+
+The function and class names follow the reference's nanobind module
+(python/pylibwholegraph/src/pylibwholegraph/binding/registrations.cpp:288-402) so that code
+written against `wholegraph_binding` reads the same here.  Only the C ABI declared in
+include/wholegraph/*.h is used; there is no Python or CPU fallback: loading fails loudly when
+the shared library is missing.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import os
+from typing import Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libwholegraph.so")
+
+MAX_TENSOR_DIM = 8
+
+
+class ErrorCode(enum.IntEnum):
+    SUCCESS = 0
+    UNKNOW_ERROR = 1
+    NOT_IMPLEMENTED = 2
+    LOGIC_ERROR = 3
+    CUDA_ERROR = 4
+    COMMUNICATION_ERROR = 5
+    INVALID_INPUT = 6
+    INVALID_VALUE = 7
+    OUT_OF_MEMORY = 8
+    NOT_SUPPORTED = 9
+    SYSTEM_ERROR = 10
+
+
+class WholeGraphDataType(enum.IntEnum):
+    DtUnknown = 0
+    DtFloat = 1
+    DtHalf = 2
+    DtDouble = 3
+    DtBF16 = 4
+    DtInt = 5
+    DtInt64 = 6
+    DtInt16 = 7
+    DtInt8 = 8
+    DtCount = 9
+
+
+class WholeGraphMemoryType(enum.IntEnum):
+    MtNone = 0
+    MtContinuous = 1
+    MtDistributed = 2
+    MtChunked = 3
+
+
+class WholeGraphMemoryLocation(enum.IntEnum):
+    MlNone = 0
+    MlDevice = 1
+    MlHost = 2
+
+
+class WholeGraphMemoryAllocType(enum.IntEnum):
+    MatNone = 0
+    MatDevice = 1
+    MatHost = 2
+    MatPinned = 3
+
+
+class WholeGraphOptimizerType(enum.IntEnum):
+    OptNone = 0
+    OptSgd = 1
+    OptLazyAdam = 2
+    OptRmsProp = 3
+    OptAdaGrad = 4
+
+
+class WholeGraphAccessType(enum.IntEnum):
+    AtNone = 0
+    AtReadOnly = 1
+    AtReadWrite = 2
+
+
+class WholeGraphError(RuntimeError):
+    def __init__(self, code: int, what: str):
+        self.code = ErrorCode(code)
+        super().__init__(f"{what} failed with {self.code.name}")
+
+
+class TensorDescription(C.Structure):
+    _fields_ = [
+        ("sizes", C.c_int64 * MAX_TENSOR_DIM),
+        ("strides", C.c_int64 * MAX_TENSOR_DIM),
+        ("storage_offset", C.c_int64),
+        ("dim", C.c_int),
+        ("dtype", C.c_int),
+    ]
+
+
+class UniqueId(C.Structure):
+    _fields_ = [("internal", C.c_char * 128)]
+
+
+CREATE_CTX_FN = C.CFUNCTYPE(None, C.POINTER(C.c_void_p), C.c_void_p)
+DESTROY_CTX_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
+MALLOC_FN = C.CFUNCTYPE(C.c_void_p, C.POINTER(TensorDescription), C.c_int, C.c_void_p, C.c_void_p)
+FREE_FN = C.CFUNCTYPE(None, C.c_void_p, C.c_void_p)
+
+
+class TempMemoryFns(C.Structure):
+    _fields_ = [
+        ("create_memory_context_fn", CREATE_CTX_FN),
+        ("destroy_memory_context_fn", DESTROY_CTX_FN),
+        ("malloc_fn", MALLOC_FN),
+        ("free_fn", FREE_FN),
+        ("global_context", C.c_void_p),
+    ]
+
+
+class OutputMemoryFns(C.Structure):
+    _fields_ = [("malloc_fn", MALLOC_FN), ("free_fn", FREE_FN), ("global_context", C.c_void_p)]
+
+
+class EnvFns(C.Structure):
+    _fields_ = [("temporary_fns", TempMemoryFns), ("output_fns", OutputMemoryFns)]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+def _declare(lib: C.CDLL) -> None:
+    vp, i64, sz = C.c_void_p, C.c_int64, C.c_size_t
+    TD = C.POINTER(TensorDescription)
+    sig = {
+        "wholegraph_init": (C.c_int, [C.c_uint, C.c_int]),
+        "wholegraph_finalize": (C.c_int, []),
+        "wholegraph_create_unique_id": (C.c_int, [C.POINTER(UniqueId)]),
+        "wholegraph_create_communicator": (C.c_int, [C.POINTER(vp), UniqueId, C.c_int, C.c_int]),
+        "wholegraph_split_communicator": (C.c_int, [C.POINTER(vp), vp, C.c_int, C.c_int]),
+        "wholegraph_destroy_communicator": (C.c_int, [vp]),
+        "wholegraph_communicator_get_rank": (C.c_int, [C.POINTER(C.c_int), vp]),
+        "wholegraph_communicator_get_size": (C.c_int, [C.POINTER(C.c_int), vp]),
+        "wholegraph_communicator_barrier": (C.c_int, [vp]),
+        "wholegraph_communicator_support_type_location": (C.c_int, [vp, C.c_int, C.c_int]),
+        "wholegraph_malloc": (C.c_int, [C.POINTER(vp), sz, vp, C.c_int, C.c_int, sz, C.POINTER(sz)]),
+        "wholegraph_free": (C.c_int, [vp]),
+        "wholegraph_get_memory_type": (C.c_int, [vp]),
+        "wholegraph_get_memory_location": (C.c_int, [vp]),
+        "wholegraph_get_total_size": (sz, [vp]),
+        "wholegraph_get_data_granularity": (sz, [vp]),
+        "wholegraph_get_local_memory": (C.c_int, [C.POINTER(vp), C.POINTER(sz), C.POINTER(sz), vp]),
+        "wholegraph_get_rank_memory": (C.c_int, [C.POINTER(vp), C.POINTER(sz), C.POINTER(sz), C.c_int, vp]),
+        "wholegraph_get_global_pointer": (C.c_int, [C.POINTER(vp), vp]),
+        "wholegraph_get_rank_partition_sizes": (C.c_int, [C.POINTER(sz), vp]),
+        "wholegraph_get_rank_partition_offsets": (C.c_int, [C.POINTER(sz), vp]),
+        "wholegraph_equal_entry_partition_plan": (C.c_int, [C.POINTER(sz), sz, C.c_int]),
+        "wholegraph_dtype_get_element_size": (sz, [C.c_int]),
+        "wholegraph_initialize_tensor_desc": (None, [TD]),
+        "wholegraph_squeeze_tensor": (C.c_bool, [TD, C.c_int]),
+        "wholegraph_unsqueeze_tensor": (C.c_bool, [TD, C.c_int]),
+        "wholegraph_get_memory_element_count_from_tensor": (i64, [TD]),
+        "wholegraph_get_memory_size_from_tensor": (i64, [TD]),
+        "wholegraph_create_tensor": (C.c_int, [C.POINTER(vp), TD, vp, C.c_int, C.c_int, C.POINTER(sz)]),
+        "wholegraph_destroy_tensor": (C.c_int, [vp]),
+        "wholegraph_make_tensor_from_pointer": (C.c_int, [C.POINTER(vp), vp, TD]),
+        "wholegraph_make_tensor_from_handle": (C.c_int, [C.POINTER(vp), vp, TD]),
+        "wholegraph_tensor_has_handle": (C.c_bool, [vp]),
+        "wholegraph_tensor_get_memory_handle": (vp, [vp]),
+        "wholegraph_tensor_get_tensor_description": (TD, [vp]),
+        "wholegraph_tensor_map_local_tensor": (C.c_int, [vp, C.POINTER(vp)]),
+        "wholegraph_tensor_get_data_pointer": (vp, [vp]),
+        "wholegraph_tensor_get_entry_offsets": (C.c_int, [C.POINTER(sz), vp]),
+        "wholegraph_tensor_get_entry_partition_sizes": (C.c_int, [C.POINTER(sz), vp]),
+        "wholegraph_tensor_get_local_entry_count": (C.c_int, [C.POINTER(sz), vp]),
+        "wholegraph_tensor_get_local_entry_start": (C.c_int, [C.POINTER(sz), vp]),
+        "wholegraph_tensor_get_subtensor": (C.c_int, [vp, C.POINTER(i64), C.POINTER(i64), C.POINTER(vp)]),
+        "wholegraph_tensor_get_root": (vp, [vp]),
+        "get_wholegraph_tensor_count": (i64, []),
+        "wholegraph_gather": (C.c_int, [vp, vp, vp, C.POINTER(EnvFns), vp, C.c_int]),
+        "wholegraph_scatter": (C.c_int, [vp, vp, vp, C.POINTER(EnvFns), vp, C.c_int]),
+        "wholegraph_b200_get_default_env_func": (C.POINTER(EnvFns), []),
+        "wholegraph_b200_get_cached_env_func": (C.POINTER(EnvFns), []),
+        "wholegraph_b200_drop_cached_env_func_memory": (None, []),
+        "wholegraph_b200_kernel_launch_count": (C.c_ulonglong, []),
+        "wholegraph_b200_version": (C.c_char_p, []),
+    }
+    optional = {
+        "wholegraph_create_embedding_optimizer": (C.c_int, [C.POINTER(vp), C.c_int]),
+        "wholegraph_optimizer_set_parameter": (C.c_int, [vp, C.c_char_p, vp]),
+        "wholegraph_destroy_embedding_optimizer": (None, [vp]),
+        "wholegraph_create_embedding_cache_policy": (C.c_int, [C.POINTER(vp), vp, C.c_int, C.c_int, C.c_int, C.c_float]),
+        "wholegraph_destroy_embedding_cache_policy": (C.c_int, [vp]),
+        "wholegraph_create_embedding": (C.c_int, [C.POINTER(vp), TD, vp, C.c_int, C.c_int, vp, C.POINTER(sz), C.c_int, C.c_int]),
+        "wholegraph_destroy_embedding": (C.c_int, [vp]),
+        "wholegraph_embedding_get_embedding_tensor": (vp, [vp]),
+        "wholegraph_embedding_set_optimizer": (C.c_int, [vp, vp]),
+        "wholegraph_embedding_gather": (C.c_int, [vp, vp, vp, C.c_bool, C.POINTER(EnvFns), i64]),
+        "wholegraph_embedding_gather_gradient_apply": (C.c_int, [vp, vp, vp, C.c_bool, C.c_float, C.POINTER(EnvFns), i64]),
+        "wholegraph_embedding_get_optimizer_state_names": (C.POINTER(C.c_char_p), [vp]),
+        "wholegraph_embedding_get_optimizer_state": (vp, [vp, C.c_char_p]),
+        "wholegraph_embedding_writeback_cache": (C.c_int, [vp, i64]),
+        "wholegraph_embedding_drop_all_cache": (C.c_int, [vp, i64]),
+        "wholegraph_load_from_file": (C.c_int, [vp, sz, sz, sz, C.POINTER(C.c_char_p), C.c_int, C.c_int]),
+        "wholegraph_store_to_file": (C.c_int, [vp, sz, sz, sz, C.c_char_p]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    for name, spec in optional.items():
+        if not hasattr(lib, name):
+            continue
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = spec
+
+
+def load_library(path: Optional[str] = None) -> C.CDLL:
+    """dlopen libwholegraph.so (RTLD_LOCAL, like the reference's libwholegraph.load_library,
+    python/libwholegraph/src/libwholegraph/load.py:38-87)."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = path or LIB_PATH
+    if not os.path.exists(p):
+        raise RuntimeError(
+            f"{p} is missing: build it with `python cugraph-gnn_b200/build.py` "
+            "(there is no CPU or Python fallback for the wholegraph ops)")
+    lib = C.CDLL(p, mode=C.RTLD_LOCAL)
+    _declare(lib)
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def lib() -> C.CDLL:
+    return load_library()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise WholeGraphError(code, what)
+
+
+# --------------------------------------------------------------------------------------------
+# thin wrappers, named after the reference's binding functions
+# --------------------------------------------------------------------------------------------
+def init(flags: int = 0, log_level: int = 3) -> None:
+    check(lib().wholegraph_init(flags, log_level), "wholegraph_init")
+
+
+def finalize() -> None:
+    check(lib().wholegraph_finalize(), "wholegraph_finalize")
+
+
+def create_unique_id() -> UniqueId:
+    uid = UniqueId()
+    check(lib().wholegraph_create_unique_id(C.byref(uid)), "wholegraph_create_unique_id")
+    return uid
+
+
+def unique_id_to_bytes(uid: UniqueId) -> bytes:
+    return C.string_at(C.addressof(uid), C.sizeof(UniqueId))
+
+
+def unique_id_from_bytes(raw: bytes) -> UniqueId:
+    uid = UniqueId()
+    C.memmove(C.addressof(uid), raw, C.sizeof(UniqueId))
+    return uid
+
+
+def create_communicator(uid: UniqueId, rank: int, size: int) -> C.c_void_p:
+    comm = C.c_void_p()
+    check(lib().wholegraph_create_communicator(C.byref(comm), uid, rank, size),
+          "wholegraph_create_communicator")
+    return comm
+
+
+def destroy_communicator(comm) -> None:
+    check(lib().wholegraph_destroy_communicator(comm), "wholegraph_destroy_communicator")
+
+
+def make_description(shape: Sequence[int], dtype: WholeGraphDataType,
+                     strides: Optional[Sequence[int]] = None, storage_offset: int = 0) -> TensorDescription:
+    d = TensorDescription()
+    lib().wholegraph_initialize_tensor_desc(C.byref(d))
+    d.dim = len(shape)
+    d.dtype = int(dtype)
+    d.storage_offset = storage_offset
+    if strides is None:
+        strides, acc = [], 1
+        for s in reversed(shape):
+            strides.insert(0, acc)
+            acc *= max(int(s), 1)
+    for i, (s, st) in enumerate(zip(shape, strides)):
+        d.sizes[i] = int(s)
+        d.strides[i] = int(st)
+    return d
+
+
+def create_wholegraph_tensor(desc: TensorDescription, comm, memory_type, memory_location,
+                             entry_partition: Optional[Sequence[int]] = None) -> C.c_void_p:
+    t = C.c_void_p()
+    part = None
+    if entry_partition is not None:
+        part = (C.c_size_t * len(entry_partition))(*entry_partition)
+    check(lib().wholegraph_create_tensor(C.byref(t), C.byref(desc), comm, int(memory_type),
+                                         int(memory_location), part), "wholegraph_create_tensor")
+    return t
+
+
+def make_tensor_from_pointer(ptr: int, desc: TensorDescription) -> C.c_void_p:
+    t = C.c_void_p()
+    check(lib().wholegraph_make_tensor_from_pointer(C.byref(t), C.c_void_p(ptr), C.byref(desc)),
+          "wholegraph_make_tensor_from_pointer")
+    return t
+
+
+def destroy_wholegraph_tensor(t) -> None:
+    check(lib().wholegraph_destroy_tensor(t), "wholegraph_destroy_tensor")
+
+
+def default_env_fns():
+    return lib().wholegraph_b200_get_default_env_func()
+
+
+def cached_env_fns():
+    return lib().wholegraph_b200_get_cached_env_func()
+
+
+def wholegraph_gather_op(wg_tensor, indices, output, env_fns, stream_int: int = 0, gather_sms: int = -1) -> None:
+    check(lib().wholegraph_gather(wg_tensor, indices, output, env_fns, C.c_void_p(stream_int), gather_sms),
+          "wholegraph_gather")
+
+
+def wholegraph_scatter_op(input_, indices, wg_tensor, env_fns, stream_int: int = 0, scatter_sms: int = -1) -> None:
+    check(lib().wholegraph_scatter(input_, indices, wg_tensor, env_fns, C.c_void_p(stream_int), scatter_sms),
+          "wholegraph_scatter")
+
+
+def local_view(wg_tensor):
+    """(pointer, rows) of this rank's shard of a handle tensor."""
+    lt = C.c_void_p()
+    check(lib().wholegraph_tensor_map_local_tensor(wg_tensor, C.byref(lt)), "wholegraph_tensor_map_local_tensor")
+    ptr = lib().wholegraph_tensor_get_data_pointer(lt)
+    rows = lib().wholegraph_tensor_get_tensor_description(lt).contents.sizes[0]
+    destroy_wholegraph_tensor(lt)
+    return ptr, rows

@@ -1,0 +1,223 @@
+"""GPU parity of wholegraph_gather / wholegraph_scatter against the CPU oracle, through the C ABI.
+
+The parameter grid follows the reference's gtest grids
+(cpp/tests/wholegraph_tensor_ops/wholegraph_gather_tests.cu:271-413,
+wholegraph_scatter_tests.cu:281-404): empty request lists, dims 1/11/32/127/128/129/513,
+row strides above the dim, storage offsets, every legal dtype pair, int32 and int64 indices,
+negative indices.  Everything is compared bit for bit.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+FLOATS = [1, 2, 3, 4]   # fp32 fp16 fp64 bf16
+INTS = [5, 6, 7, 8]     # int32 int64 int16 int8
+
+
+def _random_table(rng, orc, rows, cols, dt):
+    """Random contents as the numpy carrier dtype of wholegraph dtype `dt`."""
+    npdt = orc.np_dtype(dt)
+    if dt in (1, 3):
+        return rng.uniform(-1, 1, size=(rows, cols)).astype(npdt)
+    if dt == 2:
+        return rng.uniform(-1, 1, size=(rows, cols)).astype(np.float16)
+    if dt == 4:
+        return orc.float_to_bf16_bits(rng.uniform(-1, 1, size=(rows, cols)).astype(np.float32))
+    info = np.iinfo(npdt)
+    return rng.integers(info.min, info.max, size=(rows, cols), dtype=npdt, endpoint=True)
+
+
+def _to_device(torch, a, dt):
+    t = torch.from_numpy(a.view(np.int16) if dt == 4 else a).cuda()
+    return t.view(torch.bfloat16) if dt == 4 else t
+
+
+def _to_host(torch, t, dt):
+    if dt == 4:
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def _run_gather(gpu, wgb, orc, rng, rows, dim, stride, offset, tab_dt, out_dt, n, idx_np_dtype,
+                out_stride=None, negatives=True):
+    import torch
+    out_stride = out_stride or dim
+    storage = _random_table(rng, orc, rows, stride, tab_dt).reshape(-1)
+    pad = _random_table(rng, orc, 1, offset + 1, tab_dt).reshape(-1)[:offset]
+    storage = np.concatenate([pad, storage])
+    idx = rng.integers(0, rows, size=n).astype(idx_np_dtype)
+    if negatives and n > 3:
+        idx[rng.integers(0, n, size=max(1, n // 16))] = -1
+    d_storage = _to_device(torch, storage, tab_dt)
+    d_idx = torch.from_numpy(idx).cuda()
+    sentinel = _random_table(rng, orc, max(n, 1), out_stride, out_dt)[:n]
+    d_out = _to_device(torch, sentinel.copy(), out_dt)
+
+    desc = wgb.make_description([rows, dim], wgb.WholeGraphDataType(tab_dt), strides=[stride, 1],
+                                storage_offset=offset)
+    wt = wgb.make_tensor_from_pointer(d_storage.data_ptr(), desc)
+    odesc = wgb.make_description([n, dim], wgb.WholeGraphDataType(out_dt), strides=[out_stride, 1])
+    wo = wgb.make_tensor_from_pointer(d_out.data_ptr(), odesc)
+    wi = gpu.wrap_torch_tensor(d_idx)
+    try:
+        wgb.wholegraph_gather_op(wt, wi, wo, wgb.cached_env_fns(), gpu.current_stream_int())
+        torch.cuda.synchronize()
+    finally:
+        for t in (wt, wo, wi):
+            wgb.destroy_wholegraph_tensor(t)
+    table_view = storage[offset:offset + rows * stride].reshape(rows, stride)[:, :dim]
+    want = sentinel.copy()
+    orc.gather(table_view, idx, out_dt=out_dt, out=want[:, :dim], table_bf16=(tab_dt == 4))
+    got = _to_host(torch, d_out, out_dt)
+    assert np.array_equal(got.view(want.dtype), want)
+
+
+@pytest.mark.parametrize("dim,stride,offset", [(1, 1, 0), (11, 11, 0), (32, 32, 0), (127, 127, 0),
+                                               (128, 128, 0), (129, 129, 0), (513, 513, 0),
+                                               (128, 130, 2), (11, 12, 0), (32, 33, 1), (64, 72, 8)])
+@pytest.mark.parametrize("tab_dt,out_dt", [(1, 1), (1, 2), (1, 4), (2, 2), (2, 1), (4, 4), (4, 1)])
+def test_gather_shapes(gpu, wgb, orc, dim, stride, offset, tab_dt, out_dt):
+    rng = np.random.default_rng(dim * 1000 + stride * 10 + tab_dt * 3 + out_dt)
+    _run_gather(gpu, wgb, orc, rng, 5000, dim, stride, offset, tab_dt, out_dt, 1537, np.int64)
+
+
+@pytest.mark.parametrize("tab_dt", FLOATS)
+@pytest.mark.parametrize("out_dt", FLOATS)
+@pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
+def test_gather_float_pairs(gpu, wgb, orc, tab_dt, out_dt, idx_dtype):
+    rng = np.random.default_rng(tab_dt * 16 + out_dt)
+    for dim in (8, 30, 128):
+        _run_gather(gpu, wgb, orc, rng, 3000, dim, dim, 0, tab_dt, out_dt, 777, idx_dtype)
+
+
+@pytest.mark.parametrize("tab_dt", INTS)
+@pytest.mark.parametrize("out_dt", INTS)
+def test_gather_int_pairs(gpu, wgb, orc, tab_dt, out_dt):
+    rng = np.random.default_rng(tab_dt * 16 + out_dt)
+    for dim in (1, 16, 100):
+        _run_gather(gpu, wgb, orc, rng, 3000, dim, dim, 0, tab_dt, out_dt, 900, np.int64)
+
+
+@pytest.mark.parametrize("n", [0, 1, 31, 32, 33, 255, 257])
+def test_gather_list_lengths(gpu, wgb, orc, n):
+    rng = np.random.default_rng(n)
+    _run_gather(gpu, wgb, orc, rng, 1000, 128, 128, 0, 1, 2, n, np.int64)
+    _run_gather(gpu, wgb, orc, rng, 1000, 128, 128, 0, 2, 2, n, np.int32, out_stride=136)
+
+
+def test_gather_1d_table(gpu, wgb, orc):
+    import torch
+    rng = np.random.default_rng(5)
+    table = rng.integers(-10**12, 10**12, size=20000, dtype=np.int64)
+    idx = rng.integers(0, 20000, size=3001).astype(np.int64)
+    idx[7] = -1
+    d_table, d_idx = torch.from_numpy(table).cuda(), torch.from_numpy(idx).cuda()
+    d_out = torch.full((3001,), -5, dtype=torch.int64, device="cuda")
+    wt = gpu.wrap_torch_tensor(d_table)
+    gpu.gather(wt, d_idx, d_out)
+    torch.cuda.synchronize()
+    wgb.destroy_wholegraph_tensor(wt)
+    want = orc.gather(table, idx, out=np.full(3001, -5, dtype=np.int64))
+    assert np.array_equal(d_out.cpu().numpy(), want)
+
+
+def test_gather_rejects_bad_arguments(gpu, wgb):
+    import torch
+    table = torch.zeros((10, 4), dtype=torch.float32, device="cuda")
+    idx = torch.zeros(3, dtype=torch.int64, device="cuda")
+    wt = gpu.wrap_torch_tensor(table)
+    # float table into an integer output
+    with pytest.raises(wgb.WholeGraphError) as e:
+        gpu.gather(wt, idx, torch.zeros((3, 4), dtype=torch.int32, device="cuda"))
+    assert e.value.code == wgb.ErrorCode.LOGIC_ERROR
+    # row count mismatch
+    with pytest.raises(wgb.WholeGraphError) as e:
+        gpu.gather(wt, idx, torch.zeros((4, 4), dtype=torch.float32, device="cuda"))
+    assert e.value.code == wgb.ErrorCode.LOGIC_ERROR
+    # 1-D output for a 2-D table
+    with pytest.raises(wgb.WholeGraphError) as e:
+        gpu.gather(wt, idx, torch.zeros(3, dtype=torch.float32, device="cuda"))
+    assert e.value.code == wgb.ErrorCode.INVALID_INPUT
+    wgb.destroy_wholegraph_tensor(wt)
+
+
+@pytest.mark.parametrize("in_dt,tab_dt", [(1, 1), (2, 1), (1, 2), (4, 1), (1, 4), (3, 2), (2, 2),
+                                          (5, 6), (8, 5), (6, 7)])
+@pytest.mark.parametrize("dim,stride,offset", [(1, 1, 0), (11, 12, 0), (128, 128, 0), (129, 131, 2),
+                                               (513, 513, 0)])
+def test_scatter(gpu, wgb, orc, in_dt, tab_dt, dim, stride, offset):
+    import torch
+    rng = np.random.default_rng(in_dt * 100 + tab_dt * 10 + dim)
+    rows, n = 4000, 1111
+    storage = _random_table(rng, orc, rows + 1, stride, tab_dt).reshape(-1)
+    idx = rng.permutation(rows)[:n].astype(np.int64)  # unique: duplicate writers race
+    idx[5] = -1
+    inp = _random_table(rng, orc, n, dim, in_dt)
+    d_storage = _to_device(torch, storage.copy(), tab_dt)
+    d_in, d_idx = _to_device(torch, inp, in_dt), torch.from_numpy(idx).cuda()
+    desc = wgb.make_description([rows, dim], wgb.WholeGraphDataType(tab_dt), strides=[stride, 1],
+                                storage_offset=offset)
+    wt = wgb.make_tensor_from_pointer(d_storage.data_ptr(), desc)
+    gpu.scatter(d_in, d_idx, wt)
+    torch.cuda.synchronize()
+    wgb.destroy_wholegraph_tensor(wt)
+    want = storage.copy()
+    view = want[offset:offset + rows * stride].reshape(rows, stride)[:, :dim]
+    orc.scatter(inp, idx, view, rows_bf16=(in_dt == 4), table_bf16=(tab_dt == 4))
+    got = _to_host(torch, d_storage, tab_dt)
+    assert np.array_equal(got.view(want.dtype), want)
+
+
+def test_config1_gather_then_scatter(gpu, wgb, orc):
+    """1,000,000 x 128 fp32 table (seed 0), 65,536 int64 ids (seed 1), gather to fp32, then
+    scatter 65,536 unique-id fp32 rows (seed 2); bit-exact."""
+    import torch
+    rows, dim, n = 1_000_000, 128, 65_536
+    table = np.random.default_rng(0).uniform(-1, 1, size=(rows, dim)).astype(np.float32)
+    idx = np.random.default_rng(1).integers(0, rows, size=n, dtype=np.int64)
+    d_table, d_idx = torch.from_numpy(table).cuda(), torch.from_numpy(idx).cuda()
+    wt = gpu.wrap_torch_tensor(d_table)
+    out = torch.empty((n, dim), dtype=torch.float32, device="cuda")
+    gpu.gather(wt, d_idx, out)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), orc.gather(table, idx, threads=8))
+    rng2 = np.random.default_rng(2)
+    uniq = rng2.permutation(rows)[:n].astype(np.int64)
+    new_rows = rng2.uniform(-1, 1, size=(n, dim)).astype(np.float32)
+    gpu.scatter(torch.from_numpy(new_rows).cuda(), torch.from_numpy(uniq).cuda(), wt)
+    torch.cuda.synchronize()
+    wgb.destroy_wholegraph_tensor(wt)
+    orc.scatter(new_rows, uniq, table, threads=8)
+    assert np.array_equal(d_table.cpu().numpy(), table)
+
+
+def test_config2_cast_gather_properties(gpu, wgb, orc):
+    """10,000,000 x 128 fp32 table, 1,048,576 ids with replacement, gather with fused cast to
+    fp16 and bf16, then scatter of 1,048,576 unique-id fp16 rows.  Full-size run checked against
+    the oracle on a sample of rows and through size-independent properties: equal ids give
+    equal rows, the cast equals torch's round-to-nearest-even cast of the same rows, and a
+    scatter followed by a gather of the same ids returns the scattered rows."""
+    import torch
+    rows, dim, n = 10_000_000, 128, 1_048_576
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.empty((rows, dim), dtype=torch.float32, device="cuda").uniform_(-1, 1, generator=g)
+    idx = torch.randint(0, rows, (n,), generator=torch.Generator(device="cuda").manual_seed(1),
+                        device="cuda", dtype=torch.int64)
+    wt = gpu.wrap_torch_tensor(table)
+    for dt, wg in ((torch.float16, 2), (torch.bfloat16, 4)):
+        out = torch.empty((n, dim), dtype=dt, device="cuda")
+        gpu.gather(wt, idx, out)
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), table[idx].to(dt).view(torch.int16))
+        sample = torch.arange(0, n, 997, device="cuda")
+        want = orc.gather(table[idx[sample]].cpu().numpy(), np.arange(sample.numel()), out_dt=wg)
+        assert np.array_equal(out[sample].view(torch.int16).cpu().numpy().view(want.dtype), want)
+    uniq = torch.randperm(rows, generator=torch.Generator(device="cuda").manual_seed(2), device="cuda")[:n]
+    new_rows = torch.empty((n, dim), dtype=torch.float16, device="cuda").uniform_(-1, 1)
+    gpu.scatter(new_rows, uniq, wt)
+    back = torch.empty((n, dim), dtype=torch.float16, device="cuda")
+    gpu.gather(wt, uniq, back)
+    torch.cuda.synchronize()
+    assert torch.equal(back, new_rows)  # fp16 -> fp32 -> fp16 is the identity
+    wgb.destroy_wholegraph_tensor(wt)
