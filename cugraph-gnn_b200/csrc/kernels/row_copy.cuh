@@ -21,7 +21,6 @@ namespace wgb {
 constexpr int kRowCopyWarps       = 8;                   // warps per CTA
 constexpr int kRowCopyThreads     = kRowCopyWarps * 32;  // threads per CTA
 constexpr int kRowCopyTile        = 32;                  // list positions per warp tile
-constexpr int kRowCopyRowsInFlight = 4;                  // independent rows per lane per pass
 
 struct row_copy_params {
   const char* src;  // first element of row 0 (storage offset already applied)
@@ -102,6 +101,19 @@ __device__ __forceinline__ To convert_element(From x)
   return static_cast<To>(b);      // fp32 -> fp16 / bf16 rounds to nearest even
 }
 
+// Two fp32 values to one packed fp16x2 / bf16x2 word, round to nearest even: the same result
+// as two scalar casts, one instruction instead of two plus a pack.
+__device__ __forceinline__ unsigned pack2(float a, float b, __half*)
+{
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+__device__ __forceinline__ unsigned pack2(float a, float b, __nv_bfloat16*)
+{
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+
 template <typename From, typename To, int EPV>
 struct vector_cast {
   using in_raw  = typename raw_vec<sizeof(From) * EPV>::type;
@@ -117,9 +129,24 @@ struct vector_cast {
       To e[EPV];
     } b;
     a.raw = v;
+    constexpr bool kPacked = (EPV % 2 == 0) && sizeof(typename wide_of<From>::type) == 4 &&
+                             (sizeof(To) == 2) && (sizeof(typename wide_of<To>::type) == 4);
+    if constexpr (kPacked) {
+      // From widens to fp32, To is fp16 / bf16: convert pairs.
+      union {
+        out_raw raw;
+        unsigned w[EPV / 2];
+      } c;
 #pragma unroll
-    for (int i = 0; i < EPV; i++) b.e[i] = convert_element<From, To>(a.e[i]);
-    return b.raw;
+      for (int i = 0; i < EPV / 2; i++)
+        c.w[i] = pack2(static_cast<float>(a.e[2 * i]), static_cast<float>(a.e[2 * i + 1]),
+                       static_cast<To*>(nullptr));
+      return c.raw;
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPV; i++) b.e[i] = convert_element<From, To>(a.e[i]);
+      return b.raw;
+    }
   }
 };
 
@@ -132,8 +159,18 @@ __device__ __forceinline__ const char* chunked_row(const chunked_table& t, int64
 }
 
 // IN_BYTES / OUT_BYTES: bytes per vector on each side.  CAST::apply converts one vector.
-template <int IN_BYTES, int OUT_BYTES, typename CAST, bool CHUNKED>
-__global__ void __launch_bounds__(kRowCopyThreads)
+// Row number on one side of the copy for tile row r.
+__device__ __forceinline__ int64_t select_row(int select, int64_t id, int64_t pos, int64_t i)
+{
+  return select == ROW_BY_INDEX ? id : (select == ROW_BY_POSITION ? pos : i);
+}
+
+// ROWS: independent rows every lane keeps in flight per pass.  Addresses are recomputed from
+// the staged ids at load and at store time instead of being carried in registers: the kernel
+// stays within 64 registers, so 4 CTAs x 8 warps x ROWS rows are outstanding per SM, which is
+// what random 256..512-byte rows need to cover HBM latency at full bandwidth.
+template <int IN_BYTES, int OUT_BYTES, typename CAST, bool CHUNKED, int ROWS = 6>
+__global__ void __launch_bounds__(kRowCopyThreads, 4)
   row_copy_kernel(const row_copy_params p)
 {
   __shared__ int64_t s_index[kRowCopyWarps][kRowCopyTile];
@@ -142,11 +179,13 @@ __global__ void __launch_bounds__(kRowCopyThreads)
   const int lane          = threadIdx.x & 31;
   const int warp          = threadIdx.x >> 5;
   const int lpr           = p.lanes_per_row;
-  const int sub           = lane / lpr;       // which row of a pass this lane works on
-  const int col0          = lane % lpr;       // first vector of the row this lane moves
+  const int sub           = lane / lpr;  // which row of a pass this lane works on
+  const int col0          = lane % lpr;  // first vector of the row this lane moves
   const int rows_per_pass = 32 / lpr;
   const bool need_index   = p.src_select == ROW_BY_INDEX || p.dst_select == ROW_BY_INDEX;
   const bool need_pos     = p.src_select == ROW_BY_POSITION || p.dst_select == ROW_BY_POSITION;
+  const bool src_chunked  = CHUNKED && p.src_select == ROW_BY_INDEX;
+  const bool dst_chunked  = CHUNKED && p.dst_select == ROW_BY_INDEX;
 
   const int64_t tiles       = (p.count + kRowCopyTile - 1) / kRowCopyTile;
   const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * kRowCopyWarps + warp;
@@ -170,48 +209,37 @@ __global__ void __launch_bounds__(kRowCopyThreads)
     }
     __syncwarp();
 
-    for (int r0 = 0; r0 < kRowCopyTile; r0 += rows_per_pass * kRowCopyRowsInFlight) {
-      const char* src_row[kRowCopyRowsInFlight];
-      char* dst_row[kRowCopyRowsInFlight];
-      bool live[kRowCopyRowsInFlight];
+    for (int r0 = 0; r0 < kRowCopyTile; r0 += rows_per_pass * ROWS) {
+      for (int c = col0; c < p.vectors_per_row; c += lpr) {
+        typename raw_vec<IN_BYTES>::type v[ROWS];
+        bool live[ROWS];
 #pragma unroll
-      for (int k = 0; k < kRowCopyRowsInFlight; k++) {
-        const int r = r0 + k * rows_per_pass + sub;
-        live[k]     = false;
-        if (r < kRowCopyTile) {
-          const int64_t id  = s_index[warp][r];
-          const int64_t pos = s_position[warp][r];
-          const int64_t i   = base + r;
-          live[k]           = id >= 0;
-          const int64_t srow =
-            p.src_select == ROW_BY_INDEX ? id : (p.src_select == ROW_BY_POSITION ? pos : i);
-          const int64_t drow =
-            p.dst_select == ROW_BY_INDEX ? id : (p.dst_select == ROW_BY_POSITION ? pos : i);
-          if (CHUNKED && live[k]) {
-            if (p.src_select == ROW_BY_INDEX) {
-              src_row[k] = chunked_row(p.chunks, srow, p.src_stride_bytes, p.chunk_offset_bytes);
-              dst_row[k] = p.dst + drow * p.dst_stride_bytes;
-            } else {
-              src_row[k] = p.src + srow * p.src_stride_bytes;
-              dst_row[k] = const_cast<char*>(
-                chunked_row(p.chunks, drow, p.dst_stride_bytes, p.chunk_offset_bytes));
+        for (int k = 0; k < ROWS; k++) {
+          const int r = r0 + k * rows_per_pass + sub;
+          live[k]     = false;
+          if (r < kRowCopyTile) {
+            const int64_t id = s_index[warp][r];
+            live[k]          = id >= 0;
+            if (live[k]) {
+              const int64_t row = select_row(p.src_select, id, s_position[warp][r], base + r);
+              const char* src   = src_chunked
+                                    ? chunked_row(p.chunks, row, p.src_stride_bytes, p.chunk_offset_bytes)
+                                    : p.src + row * p.src_stride_bytes;
+              v[k] = load_row_vector<IN_BYTES>(src + static_cast<int64_t>(c) * IN_BYTES);
             }
-          } else {
-            src_row[k] = p.src + srow * p.src_stride_bytes;
-            dst_row[k] = p.dst + drow * p.dst_stride_bytes;
           }
         }
-      }
-      for (int c = col0; c < p.vectors_per_row; c += lpr) {
-        typename raw_vec<IN_BYTES>::type v[kRowCopyRowsInFlight];
 #pragma unroll
-        for (int k = 0; k < kRowCopyRowsInFlight; k++)
-          if (live[k]) v[k] = load_row_vector<IN_BYTES>(src_row[k] + static_cast<int64_t>(c) * IN_BYTES);
-#pragma unroll
-        for (int k = 0; k < kRowCopyRowsInFlight; k++)
-          if (live[k])
-            store_row_vector<OUT_BYTES>(dst_row[k] + static_cast<int64_t>(c) * OUT_BYTES,
-                                        CAST::apply(v[k]));
+        for (int k = 0; k < ROWS; k++) {
+          if (live[k]) {
+            const int r       = r0 + k * rows_per_pass + sub;
+            const int64_t row = select_row(p.dst_select, s_index[warp][r], s_position[warp][r], base + r);
+            char* dst = dst_chunked ? const_cast<char*>(chunked_row(p.chunks, row, p.dst_stride_bytes,
+                                                                    p.chunk_offset_bytes))
+                                    : p.dst + row * p.dst_stride_bytes;
+            store_row_vector<OUT_BYTES>(dst + static_cast<int64_t>(c) * OUT_BYTES, CAST::apply(v[k]));
+          }
+        }
       }
     }
     __syncwarp();

@@ -40,9 +40,14 @@ def wrap_torch_tensor(t: torch.Tensor):
     The storage pointer handed over is the tensor's data pointer, so storage_offset is 0 and
     the row stride is the torch stride (role of WrappedLocalTensor.wrap_tensor).
     """
-    if t.dim() not in (1, 2) or t.stride(-1) != 1:
-        raise ValueError("need a 1-D or 2-D tensor with unit inner stride")
-    desc = wgb.make_description(list(t.shape), TORCH_TO_WG[t.dtype], strides=list(t.stride()))
+    if t.dim() not in (1, 2):
+        raise ValueError("need a 1-D or 2-D tensor")
+    strides = list(t.stride())
+    if t.numel() == 0:  # torch reports arbitrary strides for empty tensors
+        strides = [t.shape[1], 1] if t.dim() == 2 else [1]
+    if strides[-1] != 1:
+        raise ValueError("need a tensor with unit inner stride")
+    desc = wgb.make_description(list(t.shape), TORCH_TO_WG[t.dtype], strides=strides)
     return wgb.make_tensor_from_pointer(t.data_ptr(), desc)
 
 

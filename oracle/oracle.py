@@ -89,6 +89,8 @@ def _idx_dt(idx: np.ndarray) -> int:
 
 def _matrix_params(a: np.ndarray):
     """(dim, row stride in elements) of a C-contiguous-per-row 1-D / 2-D array."""
+    if a.size == 0:  # numpy reports arbitrary strides for empty arrays
+        return (1, 1) if a.ndim == 1 else (a.shape[1], max(a.shape[1], 1))
     if a.ndim == 1:
         assert a.strides[0] == a.itemsize
         return 1, 1

@@ -51,7 +51,7 @@ def _run_gather(gpu, wgb, orc, rng, rows, dim, stride, offset, tab_dt, out_dt, n
         idx[rng.integers(0, n, size=max(1, n // 16))] = -1
     d_storage = _to_device(torch, storage, tab_dt)
     d_idx = torch.from_numpy(idx).cuda()
-    sentinel = _random_table(rng, orc, max(n, 1), out_stride, out_dt)[:n]
+    sentinel = np.ascontiguousarray(_random_table(rng, orc, max(n, 1), out_stride, out_dt)[:n])
     d_out = _to_device(torch, sentinel.copy(), out_dt)
 
     desc = wgb.make_description([rows, dim], wgb.WholeGraphDataType(tab_dt), strides=[stride, 1],
@@ -97,6 +97,19 @@ def test_gather_int_pairs(gpu, wgb, orc, tab_dt, out_dt):
     rng = np.random.default_rng(tab_dt * 16 + out_dt)
     for dim in (1, 16, 100):
         _run_gather(gpu, wgb, orc, rng, 3000, dim, dim, 0, tab_dt, out_dt, 900, np.int64)
+
+
+@pytest.mark.parametrize("tab_dt,out_dt,dim", [(1, 2, 128), (1, 4, 128), (1, 1, 128), (2, 2, 128), (4, 4, 128),
+                                               (2, 1, 128), (4, 1, 64), (1, 2, 16), (1, 1, 192), (2, 2, 384),
+                                               (1, 2, 20), (2, 4, 40), (3, 3, 8), (6, 6, 16), (8, 8, 64)])
+@pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
+def test_gather_long_lists(gpu, wgb, orc, tab_dt, out_dt, dim, idx_dtype):
+    """Request lists long enough for the bulk-copy (shared-memory staged) gather kernel,
+    including row sizes at and beyond its limits, which fall back to the register kernel."""
+    rng = np.random.default_rng(tab_dt * 7 + out_dt * 3 + dim)
+    _run_gather(gpu, wgb, orc, rng, 60000, dim, dim, 0, tab_dt, out_dt, 40001, idx_dtype)
+    _run_gather(gpu, wgb, orc, rng, 60000, dim, dim + 8, 8, tab_dt, out_dt, 9000, idx_dtype,
+                out_stride=dim + 16)
 
 
 @pytest.mark.parametrize("n", [0, 1, 31, 32, 33, 255, 257])
