@@ -181,6 +181,7 @@ def _declare(lib: C.CDLL) -> None:
         "wholegraph_b200_get_cached_env_func": (C.POINTER(EnvFns), []),
         "wholegraph_b200_drop_cached_env_func_memory": (None, []),
         "wholegraph_b200_kernel_launch_count": (C.c_ulonglong, []),
+        "wholegraph_b200_memcpy_async": (C.c_int, [vp, vp, sz, vp]),
         "wholegraph_b200_version": (C.c_char_p, []),
     }
     optional = {

@@ -322,6 +322,17 @@ int fork_get_device_count()
   return r == static_cast<ssize_t>(sizeof(n)) ? n : -1;
 }
 
+wholegraph_error_code_t wholegraph_b200_memcpy_async(void* dst, const void* src, size_t bytes,
+                                                       void* stream)
+{
+  if (bytes == 0) return WHOLEGRAPH_SUCCESS;
+  if (dst == nullptr || src == nullptr) return WHOLEGRAPH_INVALID_INPUT;
+  WGB_API_BEGIN
+  WGB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_b200_memcpy_async")
+}
+
 unsigned long long wholegraph_b200_kernel_launch_count() { return wgb::kernel_launch_count(); }
 
 const char* wholegraph_b200_version() { return "wholegraph-b200 0.1 sm_100a"; }

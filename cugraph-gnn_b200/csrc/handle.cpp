@@ -200,11 +200,13 @@ void alloc_vmm(wholegraph_handle_* h)
   page    = *std::max_element(pages.begin(), pages.end());
   b->page = page;
 
-  // Page p belongs to the rank whose logical shard contains byte p * page.
+  // Page p belongs to the rank whose logical shard contains the page's LAST byte, so the first
+  // byte of every shard of at least one page is physically on its own GPU (pointer queries on a
+  // shard's base then name the local device); the tail of a shard may sit on the next rank.
   size_t n_pages = round_up(std::max<size_t>(h->total_size, 1), page) / page;
   std::vector<size_t> first(W + 1);
   first[0] = 0;
-  for (int r = 1; r < W; r++) first[r] = std::min(n_pages, round_up(h->part_offsets[r], page) / page);
+  for (int r = 1; r < W; r++) first[r] = std::min(n_pages, h->part_offsets[r] / page);
   first[W] = n_pages;
   for (int r = 1; r <= W; r++) first[r] = std::max(first[r], first[r - 1]);
   b->va_size = n_pages * page;
@@ -218,6 +220,8 @@ void alloc_vmm(wholegraph_handle_* h)
 
   int me     = c->world_rank;
   int own_fd = -1;
+  WGB_DEBUG("vmm handle %d: page %zu, %zu pages, rank %d maps [%zu, +%zu)", h->id, page, n_pages, me,
+            b->map_off[me], b->map_len[me]);
   if (b->map_len[me] > 0) {
     WGB_CU_CHECK(drv().MemCreate(&b->mem[me], b->map_len[me], &prop, 0));
     WGB_CU_CHECK(drv().MemExportToShareableHandle(&own_fd, b->mem[me],
@@ -258,6 +262,7 @@ void alloc_vmm(wholegraph_handle_* h)
     c->barrier();  // nobody closes a socket that still has senders
   }
   if (own_fd >= 0) close(own_fd);
+  WGB_DEBUG("vmm handle %d: descriptors exchanged", h->id);
 
   CUdeviceptr va = 0;
   WGB_CU_CHECK(drv().MemAddressReserve(&va, b->va_size, page, 0, 0));
@@ -272,6 +277,7 @@ void alloc_vmm(wholegraph_handle_* h)
   acc.flags         = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
   WGB_CU_CHECK(drv().MemSetAccess(va, b->va_size, &acc, 1));
   h->local_ptr = static_cast<char*>(h->global_base) + h->part_offsets[me];
+  WGB_DEBUG("vmm handle %d: mapped %zu bytes at %p", h->id, b->va_size, h->global_base);
 }
 
 void free_vmm(wholegraph_handle_* h)
@@ -408,8 +414,14 @@ wholegraph_handle_* create_handle(size_t total_size, wholegraph_comm_* comm,
   // All ranks must ask for the same thing (reference: memory_handle.cpp:1408-1414).
   struct {
     size_t total, gran;
-    int type, loc, has_part;
-  } param{total_size, granularity, type, location, rank_entry_partition != nullptr};
+    int type, loc, has_part, pad;
+  } param;
+  memset(&param, 0, sizeof(param));  // compared bytewise: no indeterminate padding
+  param.total    = total_size;
+  param.gran     = granularity;
+  param.type     = type;
+  param.loc      = location;
+  param.has_part = rank_entry_partition != nullptr ? 1 : 0;
   if (!comm->all_same(&param, sizeof(param)))
     throw comm_error("wholegraph_malloc called with different arguments on different ranks");
   if (rank_entry_partition != nullptr &&

@@ -92,6 +92,35 @@ def local_shard_as_torch(wg_tensor) -> torch.Tensor:
     return view_device_memory(ptr or 0, shape, dtype, strides)
 
 
+def write_local_shard(wg_tensor, rows: torch.Tensor, first_local_row: int = 0) -> None:
+    """Copy `rows` (contiguous, same dtype and row width as the table's storage rows) into this
+    rank's shard starting at local row `first_local_row`, on the current stream.  Goes through the
+    C ABI with raw pointers, so it also works where the shard cannot be viewed as a torch tensor."""
+    lib = wgb.lib()
+    lt = C.c_void_p()
+    wgb.check(lib.wholegraph_tensor_map_local_tensor(wg_tensor, C.byref(lt)), "map_local_tensor")
+    try:
+        d = lib.wholegraph_tensor_get_tensor_description(lt).contents
+        ptr = lib.wholegraph_tensor_get_data_pointer(lt)
+        stride = d.strides[0] if d.dim == 2 else 1
+        width = d.sizes[1] if d.dim == 2 else 1
+        local_rows = d.sizes[0]
+    finally:
+        wgb.destroy_wholegraph_tensor(lt)
+    if rows.numel() == 0:
+        return
+    if not rows.is_contiguous() or TORCH_TO_WG[rows.dtype] != DT(d.dtype):
+        raise ValueError("rows must be contiguous and of the table dtype")
+    if stride != width or (rows.dim() == 2 and rows.shape[1] != width):
+        raise ValueError("write_local_shard needs densely packed rows")
+    if first_local_row + rows.shape[0] > local_rows:
+        raise ValueError("rows exceed the local shard")
+    nbytes = rows.numel() * rows.element_size()
+    dst = ptr + first_local_row * stride * rows.element_size()
+    wgb.check(lib.wholegraph_b200_memcpy_async(C.c_void_p(dst), C.c_void_p(rows.data_ptr()), nbytes,
+                                               C.c_void_p(current_stream_int())), "memcpy_async")
+
+
 def gather(wg_table, indices: torch.Tensor, out: torch.Tensor, env=None, sms: int = -1) -> torch.Tensor:
     """out[i] = cast(table[indices[i]]) on the current stream (role of WholeGraphTensor.gather,
     python/wholegraph-torch/src/wholegraph_torch/tensor.py:52-73)."""

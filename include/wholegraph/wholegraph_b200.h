@@ -26,6 +26,13 @@ wholegraph_env_func_t* wholegraph_b200_get_cached_env_func();
 /* Return every block of the caching allocator to CUDA (synchronizes the device first). */
 void wholegraph_b200_drop_cached_env_func_memory();
 
+/*
+ * cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, stream) for callers that hold raw
+ * pointers (a shard of a handle, a ctypes buffer) but no CUDA runtime binding of their own.
+ */
+wholegraph_error_code_t wholegraph_b200_memcpy_async(void* dst, const void* src, size_t bytes,
+                                                       void* stream);
+
 /* Number of kernels this library has launched in this process since load. */
 unsigned long long wholegraph_b200_kernel_launch_count();
 

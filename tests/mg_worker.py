@@ -1,0 +1,146 @@
+"""One rank of the multi-GPU parity tests (started by tests/test_multi_gpu.py, one process per GPU).
+
+Rendezvous is a file: rank 0 writes the communicator's unique id, the others read it.  Every
+scenario compares against the CPU oracle evaluated on a closed-form table that each rank can
+rebuild on the host.
+"""
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def table_values(rows, dim, np_dtype):
+    r = np.arange(rows, dtype=np.int64)[:, None]
+    c = np.arange(dim, dtype=np.int64)[None, :]
+    if np.issubdtype(np_dtype, np.integer):
+        return ((r * 131 + c * 7) % 20011 - 10000).astype(np_dtype)
+    return (((r * 131 + c * 7) % 2001 - 1000) / 1000.0).astype(np.float32).astype(np_dtype)
+
+
+def main():
+    rank, world, rdv = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    scenario = sys.argv[4]
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("WG_TEST_STACK_AFTER", "90")), exit=True)
+    import torch
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    wgb = pkg.binding
+    from cugraph_gnn_b200 import torch_utils as tu
+    from oracle import oracle as orc
+    wgb.load_library()
+    torch.cuda.set_device(rank)
+    wgb.init(0, int(os.environ.get("WG_TEST_LOG_LEVEL", "2")))
+
+    uid_path = os.path.join(rdv, "uid.bin")
+    if rank == 0:
+        raw = wgb.unique_id_to_bytes(wgb.create_unique_id())
+        with open(uid_path + ".tmp", "wb") as f:
+            f.write(raw)
+        os.rename(uid_path + ".tmp", uid_path)
+    else:
+        deadline = time.time() + 120
+        while not os.path.exists(uid_path):
+            if time.time() > deadline:
+                raise RuntimeError("rendezvous file never appeared")
+            time.sleep(0.05)
+        with open(uid_path, "rb") as f:
+            raw = f.read()
+    comm = wgb.create_communicator(wgb.unique_id_from_bytes(raw), rank, world)
+    MT, ML, DT = wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphDataType
+    env = wgb.cached_env_fns()
+
+    def make_table(mem_type, rows, dim, tdt, partition=None, location=ML.MlDevice):
+        desc = wgb.make_description([rows, dim], DT(tu.TORCH_TO_WG[tdt]))
+        t = wgb.create_wholegraph_tensor(desc, comm, mem_type, location, partition)
+        start, count = wgb.C.c_size_t(), wgb.C.c_size_t()
+        wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_start(wgb.C.byref(start), t), "entry_start")
+        wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_count(wgb.C.byref(count), t), "entry_count")
+        npdt = np.float32 if tdt in (torch.float32, torch.float16, torch.bfloat16) else np.int64
+        full = table_values(rows, dim, npdt)
+        local = torch.from_numpy(full[start.value:start.value + count.value]).cuda().to(tdt).contiguous()
+        tu.write_local_shard(t, local)
+        torch.cuda.synchronize()
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        return t, full
+
+    def host_table(full, tdt):
+        if tdt == torch.float16:
+            return full.astype(np.float16), False
+        if tdt == torch.bfloat16:
+            return orc.float_to_bf16_bits(full), True
+        return full, False
+
+    def to_host(t):
+        return t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy()
+
+    def check_gather(mem_type, rows, dim, tdt, odt, n, partition=None, idx_dtype=torch.int64, seed=0):
+        print(f"rank {rank}: gather {mem_type.name} rows={rows} dim={dim} {tdt}->{odt} n={n}", flush=True)
+        t, full = make_table(mem_type, rows, dim, tdt, partition)
+        g = torch.Generator(device="cuda").manual_seed(1000 * seed + rank)
+        idx = torch.randint(0, rows, (n,), generator=g, device="cuda").to(idx_dtype)
+        if n > 10:
+            idx[::37] = -1
+        out = torch.full((n, dim), 3, dtype=odt, device="cuda")
+        tu.gather(t, idx, out, env)
+        torch.cuda.synchronize()
+        tab, tab_bf16 = host_table(full, tdt)
+        want = np.full((n, dim), 3, dtype=np.float32)
+        want = to_host(torch.from_numpy(want).to(odt)) if odt != torch.float32 else want
+        want = np.ascontiguousarray(want)
+        orc.gather(tab, idx.cpu().numpy(), out_dt=int(tu.TORCH_TO_WG[odt]), out=want, table_bf16=tab_bf16)
+        got = to_host(out)
+        assert np.array_equal(got.view(want.dtype), want), f"gather {mem_type.name} {tdt}->{odt} n={n} differs on rank {rank}"
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        wgb.destroy_wholegraph_tensor(t)
+
+    def check_scatter(mem_type, rows, dim, tdt, idt, n_per_rank):
+        print(f"rank {rank}: scatter {mem_type.name} rows={rows} dim={dim} {idt}->{tdt}", flush=True)
+        t, full = make_table(mem_type, rows, dim, tdt)
+        # globally unique ids: rank r takes ids congruent to r modulo world
+        rng = np.random.default_rng(7)
+        perm = rng.permutation(rows)
+        mine = np.ascontiguousarray(perm[rank::world][:n_per_rank]).astype(np.int64)
+        vals = np.random.default_rng(100 + rank).uniform(-1, 1, size=(mine.shape[0], dim)).astype(np.float32)
+        d_vals = torch.from_numpy(vals).cuda().to(idt)
+        tu.scatter(d_vals, torch.from_numpy(mine).cuda(), t, env)
+        torch.cuda.synchronize()
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        # expected table after every rank's scatter
+        tab, tab_bf16 = host_table(full, tdt)
+        tab = tab.copy()
+        for r in range(world):
+            ids_r = np.ascontiguousarray(perm[r::world][:n_per_rank]).astype(np.int64)
+            vals_r = np.random.default_rng(100 + r).uniform(-1, 1, size=(ids_r.shape[0], dim)).astype(np.float32)
+            rows_r = to_host(torch.from_numpy(vals_r).to(idt))
+            orc.scatter(np.ascontiguousarray(rows_r), ids_r, tab, rows_bf16=(idt == torch.bfloat16), table_bf16=tab_bf16)
+        # read everything back through a gather of all rows
+        all_ids = torch.arange(rows, device="cuda", dtype=torch.int64)
+        back = torch.empty((rows, dim), dtype=tdt, device="cuda")
+        tu.gather(t, all_ids, back, env)
+        torch.cuda.synchronize()
+        assert np.array_equal(to_host(back).view(tab.dtype), tab), f"scatter {mem_type.name} differs on rank {rank}"
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        wgb.destroy_wholegraph_tensor(t)
+
+    mem = {"continuous": MT.MtContinuous, "distributed": MT.MtDistributed, "chunked": MT.MtChunked}[scenario]
+    check_gather(mem, 100_003, 128, torch.float16, torch.float16, 50_000, seed=1)
+    check_gather(mem, 100_003, 128, torch.float32, torch.float16, 20_001, seed=2)
+    check_gather(mem, 40_000, 33, torch.float32, torch.bfloat16, 7_777, idx_dtype=torch.int32, seed=3)
+    check_gather(mem, 1_000, 8, torch.int64, torch.int64, 0, seed=4)
+    check_gather(mem, 5 * world + 3, 16, torch.bfloat16, torch.float32, 999, seed=5)
+    part = [1000 + 10 * r for r in range(world)]
+    check_gather(mem, sum(part), 64, torch.float32, torch.float32, 12_345, partition=part, seed=6)
+    check_scatter(mem, 30_011, 128, torch.float32, torch.float16, 4_000)
+    check_scatter(mem, 9_000, 20, torch.bfloat16, torch.float32, 2_000)
+    wgb.destroy_communicator(comm)
+    print(f"rank {rank} ok", flush=True)
+
+
+if __name__ == "__main__":
+    main()
