@@ -236,11 +236,17 @@ def main():
     desc = wgb.make_description([rows, ROW_DIM], tab_wg)
     table = wgb.create_wholegraph_tensor(desc, comm, wgb.WholeGraphMemoryType.MtContinuous,
                                          wgb.WholeGraphMemoryLocation.MlDevice)
-    shard = tu.local_shard_as_torch(table)
+    local_rows = wgb.C.c_size_t()
+    wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_count(wgb.C.byref(local_rows), table), "entry_count")
+    local_rows = local_rows.value
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
     chunk = 4_000_000
-    for s in range(0, shard.shape[0], chunk):  # fill in pieces: uniform_ on fp16 makes fp32 temporaries
-        shard[s:s + chunk].uniform_(-1, 1, generator=gen)
+    for s in range(0, local_rows, chunk):  # fill in pieces through the C ABI (raw shard pointer)
+        rows_now = min(chunk, local_rows - s)
+        piece = torch.empty((rows_now, ROW_DIM), dtype=torch.float32, device="cuda").uniform_(-1, 1, generator=gen)
+        tu.write_local_shard(table, piece.to(tab_dtype).contiguous(), s)
+        del piece
+    torch.cuda.synchronize()
 
     batches = []
     if workload == "c2":
@@ -345,7 +351,12 @@ def main():
     if not multi and not args.no_cpu_baseline and rank == 0:
         from oracle import oracle as orc
         sample_rows = min(rows, 2_000_000)
-        table_np = shard[:sample_rows].cpu().numpy()
+        sample_ids = torch.arange(sample_rows, device="cuda", dtype=torch.int64)
+        sample = torch.empty((sample_rows, ROW_DIM), dtype=tab_dtype, device="cuda")
+        tu.gather(table, sample_ids, sample, env)
+        torch.cuda.synchronize()
+        table_np = sample.cpu().numpy()
+        del sample, sample_ids
         idx_np = (batches[0] % sample_rows).cpu().numpy()
         threads = os.cpu_count() or 1
         gbs, best, reps = cpu_oracle_gather_rate(table_np, idx_np, orc.DT_HALF, threads)

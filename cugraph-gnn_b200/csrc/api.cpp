@@ -12,6 +12,7 @@
 #include "comm.hpp"
 #include "common.hpp"
 #include "handle.hpp"
+#include "kernels/partition.hpp"
 #include "kernels/row_copy.hpp"
 
 static bool g_inited = false;
@@ -331,6 +332,37 @@ wholegraph_error_code_t wholegraph_b200_memcpy_async(void* dst, const void* src,
   WGB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
   return WHOLEGRAPH_SUCCESS;
   WGB_API_END("wholegraph_b200_memcpy_async")
+}
+
+size_t wholegraph_b200_partition_workspace_bytes(int64_t n, int world)
+{
+  return wgb::partition_workspace_bytes(n, world);
+}
+
+wholegraph_error_code_t wholegraph_b200_partition_by_owner(const void* ids,
+                                                             int ids_are_64,
+                                                             int64_t n,
+                                                             const int64_t* first_row,
+                                                             int world,
+                                                             void* workspace,
+                                                             size_t workspace_bytes,
+                                                             int64_t* sorted_ids,
+                                                             int64_t* positions,
+                                                             int64_t* counts,
+                                                             int64_t* starts,
+                                                             void* stream)
+{
+  if (n < 0 || first_row == nullptr || counts == nullptr || starts == nullptr)
+    return WHOLEGRAPH_INVALID_INPUT;
+  if (n > 0 && (ids == nullptr || workspace == nullptr || sorted_ids == nullptr || positions == nullptr))
+    return WHOLEGRAPH_INVALID_INPUT;
+  if (world < 1 || world > wgb::kMaxPartitionRanks) return WHOLEGRAPH_INVALID_VALUE;
+  if (workspace_bytes < wgb::partition_workspace_bytes(n, world)) return WHOLEGRAPH_INVALID_VALUE;
+  WGB_API_BEGIN
+  wgb::partition_by_owner(ids, ids_are_64 != 0, n, first_row, world, workspace, sorted_ids, positions,
+                          counts, starts, static_cast<cudaStream_t>(stream));
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_b200_partition_by_owner")
 }
 
 unsigned long long wholegraph_b200_kernel_launch_count() { return wgb::kernel_launch_count(); }

@@ -6,6 +6,8 @@
  */
 #pragma once
 
+#include <stdint.h>
+
 #include <wholegraph/env_func_ptrs.h>
 #include <wholegraph/wholegraph.h>
 
@@ -32,6 +34,34 @@ void wholegraph_b200_drop_cached_env_func_memory();
  */
 wholegraph_error_code_t wholegraph_b200_memcpy_async(void* dst, const void* src, size_t bytes,
                                                        void* stream);
+
+/*
+ * Stable partition of a request list by owning rank, the first step of every DISTRIBUTED op
+ * (role of the reference's internal bucket_and_exchange_ids_func,
+ * cpp/src/wholegraph_tensor_ops/functions/exchange_ids_nccl_func.cu:146-215, which has no C entry
+ * point of its own).
+ *   ids            n row ids, int32 (ids_are_64 = 0) or int64, device memory
+ *   first_row      HOST array of world + 1 first rows per rank; first_row[world] = table rows
+ *   workspace      device scratch of at least wholegraph_b200_partition_workspace_bytes(n, world)
+ *   sorted_ids     out, n int64 (device): ids grouped by owner, list order kept inside a group
+ *   positions      out, n int64 (device): list position each sorted id came from
+ *   counts, starts out, world int64 each (device): size and first slot of every group
+ * Ids that are negative or >= first_row[world] belong to no group and are dropped; the groups
+ * are packed at the front of the outputs.  n < 2^31, world <= 64.  Asynchronous on `stream`.
+ */
+size_t wholegraph_b200_partition_workspace_bytes(int64_t n, int world);
+wholegraph_error_code_t wholegraph_b200_partition_by_owner(const void* ids,
+                                                             int ids_are_64,
+                                                             int64_t n,
+                                                             const int64_t* first_row,
+                                                             int world,
+                                                             void* workspace,
+                                                             size_t workspace_bytes,
+                                                             int64_t* sorted_ids,
+                                                             int64_t* positions,
+                                                             int64_t* counts,
+                                                             int64_t* starts,
+                                                             void* stream);
 
 /* Number of kernels this library has launched in this process since load. */
 unsigned long long wholegraph_b200_kernel_launch_count();
