@@ -185,6 +185,8 @@ def _declare(lib: C.CDLL) -> None:
         "wholegraph_b200_partition_workspace_bytes": (sz, [i64, C.c_int]),
         "wholegraph_b200_partition_by_owner": (C.c_int, [vp, C.c_int, i64, C.POINTER(i64), C.c_int, vp, sz,
                                                          vp, vp, vp, vp, vp]),
+        "wholegraph_b200_partition_by_owner_no_alloc": (C.c_int, [vp, C.c_int, i64, C.POINTER(i64), C.c_int,
+                                                                  vp, vp, vp, vp, vp]),
         "wholegraph_b200_version": (C.c_char_p, []),
     }
     optional = {

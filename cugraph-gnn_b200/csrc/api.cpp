@@ -365,6 +365,30 @@ wholegraph_error_code_t wholegraph_b200_partition_by_owner(const void* ids,
   WGB_API_END("wholegraph_b200_partition_by_owner")
 }
 
+wholegraph_error_code_t wholegraph_b200_partition_by_owner_no_alloc(const void* ids,
+                                                                      int ids_are_64,
+                                                                      int64_t n,
+                                                                      const int64_t* first_row,
+                                                                      int world,
+                                                                      int64_t* sorted_ids,
+                                                                      int64_t* positions,
+                                                                      int64_t* counts,
+                                                                      int64_t* starts,
+                                                                      void* stream)
+{
+  if (n < 0 || first_row == nullptr || counts == nullptr || starts == nullptr)
+    return WHOLEGRAPH_INVALID_INPUT;
+  if (n > 0 && (ids == nullptr || sorted_ids == nullptr || positions == nullptr))
+    return WHOLEGRAPH_INVALID_INPUT;
+  if (world < 1 || world > wgb::kMaxPartitionRanks) return WHOLEGRAPH_INVALID_VALUE;
+  WGB_API_BEGIN
+  wgb::partition_by_owner_builtin_scratch(ids, ids_are_64 != 0, n, first_row, world, sorted_ids,
+                                          positions, counts, starts,
+                                          static_cast<cudaStream_t>(stream));
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_b200_partition_by_owner_no_alloc")
+}
+
 unsigned long long wholegraph_b200_kernel_launch_count() { return wgb::kernel_launch_count(); }
 
 const char* wholegraph_b200_version() { return "wholegraph-b200 0.1 sm_100a"; }

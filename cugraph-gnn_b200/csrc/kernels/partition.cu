@@ -12,6 +12,7 @@
 #include "partition.hpp"
 
 #include <algorithm>
+#include <mutex>
 
 #include "../common.hpp"
 #include "row_copy.hpp"
@@ -191,6 +192,52 @@ __global__ void partition_save_last_kernel(const int* hist, int64_t total, int* 
 }
 
 }  // namespace
+
+// Built-in scratch of the allocation-free entry point.  It lives in every GPU context that loads
+// this library, from load until exit.  In host code this name is only a handle for the runtime
+// (cudaGetSymbolAddress); it is not an address a kernel could be given.
+constexpr size_t kBuiltinScratchBytes = 66048;  // 64.5 KiB: 4,194,304 ids at 8 ranks
+static __device__ __align__(256) unsigned char g_builtin_partition_scratch[kBuiltinScratchBytes];
+
+// Device address of the built-in scratch on the current device, looked up once per device.
+static void* builtin_scratch_of_current_device()
+{
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static void* address[kMaxDevices] = {};
+  int dev = -1;
+  WGB_CUDA_CHECK(cudaGetDevice(&dev));
+  WGB_EXPECTS(dev >= 0 && dev < kMaxDevices, "device ordinal %d is out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (address[dev] == nullptr) {
+    void* p = nullptr;
+    WGB_CUDA_CHECK(cudaGetSymbolAddress(&p, g_builtin_partition_scratch));
+    address[dev] = p;
+  }
+  return address[dev];
+}
+
+size_t partition_builtin_scratch_bytes() { return kBuiltinScratchBytes; }
+
+void partition_by_owner_builtin_scratch(const void* ids, bool ids_are_64, int64_t n,
+                                        const int64_t* first_row, int world, int64_t* sorted_ids,
+                                        int64_t* positions, int64_t* counts, int64_t* starts,
+                                        cudaStream_t stream)
+{
+  WGB_EXPECTS(world >= 1 && world <= kMaxPartitionRanks, "world size %d exceeds %d", world,
+              kMaxPartitionRanks);
+  const size_t need = partition_workspace_bytes(n, world);
+  if (need > kBuiltinScratchBytes) {
+    throw invalid_input(WHOLEGRAPH_INVALID_VALUE,
+                        format_string("%ld ids over %d ranks need %zu bytes of scratch, the built-in "
+                                      "scratch holds %zu; use the entry point that takes a workspace",
+                                      (long)n, world, need, kBuiltinScratchBytes));
+  }
+  // Every scratch word the kernels read is written earlier in the same call, so nothing has to
+  // be cleared between calls.
+  partition_by_owner(ids, ids_are_64, n, first_row, world, builtin_scratch_of_current_device(),
+                     sorted_ids, positions, counts, starts, stream);
+}
 
 size_t partition_workspace_bytes(int64_t n, int world)
 {

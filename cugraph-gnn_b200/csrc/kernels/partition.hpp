@@ -25,4 +25,14 @@ void partition_by_owner(const void* ids, bool ids_are_64, int64_t n, const int64
                         int world, void* workspace, int64_t* sorted_ids, int64_t* positions,
                         int64_t* counts, int64_t* starts, cudaStream_t stream);
 
+// Same result as partition_by_owner, with the scratch taken from a fixed array inside the
+// library instead of from the caller.  Throws invalid_input(WHOLEGRAPH_INVALID_VALUE) when
+// partition_workspace_bytes(n, world) exceeds partition_builtin_scratch_bytes().  The first call
+// on a device looks the array's address up; calls that overlap on one GPU race on the array.
+size_t partition_builtin_scratch_bytes();
+void partition_by_owner_builtin_scratch(const void* ids, bool ids_are_64, int64_t n,
+                                        const int64_t* first_row, int world, int64_t* sorted_ids,
+                                        int64_t* positions, int64_t* counts, int64_t* starts,
+                                        cudaStream_t stream);
+
 }  // namespace wgb

@@ -63,6 +63,39 @@ wholegraph_error_code_t wholegraph_b200_partition_by_owner(const void* ids,
                                                              int64_t* starts,
                                                              void* stream);
 
+/*
+ * wholegraph_b200_partition_by_owner without any allocation, by this call or asked of the
+ * caller.  It has no counterpart in the reference.
+ *
+ * Who needs it: callers that must not reach the CUDA allocator while they run - a serving
+ * loop whose device memory is already handed out in full to its own pool, or a step that
+ * cannot afford the device-wide stall a cudaMalloc / cudaFree brings - and that therefore have
+ * no workspace to pass either.  The caller still owns ids and all four outputs; only the
+ * scratch moves into the library: a fixed 66,048-byte (64.5 KiB) array in device memory, held
+ * by every GPU that loads the library until the process exits.
+ *
+ * Limit: wholegraph_b200_partition_workspace_bytes(n, world) must not exceed 66,048, i.e.
+ * ceil(n / 2048) * world <= 16,508 (4,194,304 ids at 8 ranks, 33 million ids at 1 rank).
+ * Larger requests return WHOLEGRAPH_INVALID_VALUE and launch nothing.
+ *
+ * The first call on a device looks up the array's device address (a one-time set-up inside
+ * the CUDA runtime); make that call before starting any stream capture.  All calls on a GPU
+ * share the one array, which keeps whatever the previous call left in it: nothing needs
+ * clearing, because each call writes every word before reading it, but two calls that overlap
+ * on the GPU (different streams, no ordering) race on it and corrupt each other's result.
+ * Outputs, argument meaning and asynchrony are those of wholegraph_b200_partition_by_owner.
+ */
+wholegraph_error_code_t wholegraph_b200_partition_by_owner_no_alloc(const void* ids,
+                                                                      int ids_are_64,
+                                                                      int64_t n,
+                                                                      const int64_t* first_row,
+                                                                      int world,
+                                                                      int64_t* sorted_ids,
+                                                                      int64_t* positions,
+                                                                      int64_t* counts,
+                                                                      int64_t* starts,
+                                                                      void* stream);
+
 /* Number of kernels this library has launched in this process since load. */
 unsigned long long wholegraph_b200_kernel_launch_count();
 
