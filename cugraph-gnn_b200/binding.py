@@ -349,3 +349,60 @@ def local_view(wg_tensor):
     rows = lib().wholegraph_tensor_get_tensor_description(lt).contents.sizes[0]
     destroy_wholegraph_tensor(lt)
     return ptr, rows
+
+
+# ---- embeddings and sparse optimizers ------------------------------------------------------
+def create_embedding(desc: TensorDescription, comm, memory_type, memory_location, cache_policy=None,
+                     entry_partition: Optional[Sequence[int]] = None, user_defined_sms: int = -1,
+                     round_robin_size: int = 0) -> C.c_void_p:
+    e = C.c_void_p()
+    part = None
+    if entry_partition is not None:
+        part = (C.c_size_t * len(entry_partition))(*entry_partition)
+    check(lib().wholegraph_create_embedding(C.byref(e), C.byref(desc), comm, int(memory_type),
+                                            int(memory_location), cache_policy, part, user_defined_sms,
+                                            round_robin_size), "wholegraph_create_embedding")
+    return e
+
+
+def destroy_embedding(e) -> None:
+    check(lib().wholegraph_destroy_embedding(e), "wholegraph_destroy_embedding")
+
+
+def create_optimizer(opt_type: WholeGraphOptimizerType, **params: float) -> C.c_void_p:
+    o = C.c_void_p()
+    check(lib().wholegraph_create_embedding_optimizer(C.byref(o), int(opt_type)),
+          "wholegraph_create_embedding_optimizer")
+    for name, value in params.items():
+        v = C.c_float(value)
+        check(lib().wholegraph_optimizer_set_parameter(o, name.encode(), C.byref(v)),
+              f"wholegraph_optimizer_set_parameter({name})")
+    return o
+
+
+def embedding_tensor(e) -> C.c_void_p:
+    return C.c_void_p(lib().wholegraph_embedding_get_embedding_tensor(e))
+
+
+def embedding_state_names(e) -> list:
+    names, arr, i = [], lib().wholegraph_embedding_get_optimizer_state_names(e), 0
+    while arr and arr[i] is not None:
+        names.append(arr[i].decode())
+        i += 1
+    return names
+
+
+def embedding_state(e, name: str) -> C.c_void_p:
+    return C.c_void_p(lib().wholegraph_embedding_get_optimizer_state(e, name.encode()))
+
+
+def EmbeddingGatherForward(e, indices, output, adjust_cache: bool, env_fns, stream_int: int = 0) -> None:
+    check(lib().wholegraph_embedding_gather(e, indices, output, adjust_cache, env_fns, stream_int),
+          "wholegraph_embedding_gather")
+
+
+def EmbeddingGatherGradientApply(e, indices, grads, adjust_cache: bool, lr: float, env_fns,
+                                 stream_int: int = 0) -> None:
+    check(lib().wholegraph_embedding_gather_gradient_apply(e, indices, grads, adjust_cache, lr, env_fns,
+                                                           stream_int),
+          "wholegraph_embedding_gather_gradient_apply")

@@ -1,0 +1,415 @@
+// Sparse SGD / Lazy Adam / AdaGrad / RMSProp apply fused with duplicate-gradient reduction.
+//
+//   1. keys_kernel        local row id (or a sentinel) and list position per gradient row
+//   2. cub radix sort     (key, position) pairs, only the bits a local row id can use; stable, so
+//                         equal ids keep their arrival order
+//   3. heads_kernel       compacts the first element of every run of equal keys
+//   4. apply_kernel       one warp per distinct row: walks its run, adds the gradient rows in
+//                         arrival order (fp32, 16-byte loads, 4 rows in flight), then reads
+//                         weights and state once, updates them and writes them back
+//
+// The summed gradients never go to memory (the reference writes them to a [unique, dim] fp32
+// buffer and reads them back).  Arithmetic follows the reference kernels
+// (embedding_optimizer_func.cu:203-214 SGD, :386-421 Lazy Adam, :655-671 AdaGrad, :865-881
+// RMSProp) with every operation rounded separately (no fused multiply-add), which is also what
+// the reference's CPU test optimizer computes.
+#include "sparse_optimizer.hpp"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cub/device/device_radix_sort.cuh>
+
+#include "../common.hpp"
+#include "row_copy.hpp"
+
+namespace wgb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__global__ void keys_kernel(const void* ids, int is64, int64_t n, int64_t local_start,
+                            int64_t local_rows, uint32_t* keys, int32_t* positions)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t id = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
+                          : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
+  const int64_t r  = id - local_start;
+  keys[i]         = (r >= 0 && r < local_rows) ? static_cast<uint32_t>(r) : static_cast<uint32_t>(local_rows);
+  positions[i]    = static_cast<int32_t>(i);
+}
+
+// heads[slot] = index (in sorted order) of the first element of a run; *head_count = runs.
+__global__ void heads_kernel(const uint32_t* keys, int64_t n, uint32_t sentinel, int32_t* heads,
+                             int32_t* head_count)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  bool head       = false;
+  if (i < n) {
+    const uint32_t k = keys[i];
+    head             = k != sentinel && (i == 0 || keys[i - 1] != k);
+  }
+  const unsigned m = __ballot_sync(0xffffffffu, head);
+  if (m == 0) return;
+  const int lane = threadIdx.x & 31;
+  int base       = 0;
+  if (lane == __ffs(m) - 1) base = atomicAdd(head_count, __popc(m));
+  base = __shfl_sync(0xffffffffu, base, __ffs(m) - 1);
+  if (head) heads[base + __popc(m & ((1u << lane) - 1u))] = static_cast<int32_t>(i);
+}
+
+template <typename T>
+__device__ __forceinline__ float load_weight(const T* p)
+{
+  return static_cast<float>(*p);
+}
+template <typename T>
+__device__ __forceinline__ void store_weight(T* p, float v)
+{
+  *p = static_cast<T>(v);  // fp16 / bf16: round to nearest even
+}
+
+// VEC consecutive elements as fp32, with one vector access when VEC = 4.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[VEC])
+{
+  if constexpr (VEC == 4 && sizeof(T) == 4) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x, out[1] = v.y, out[2] = v.z, out[3] = v.w;
+  } else if constexpr (VEC == 4 && sizeof(T) == 2) {
+    union {
+      uint2 raw;
+      T e[4];
+    } u;
+    u.raw = *reinterpret_cast<const uint2*>(p);
+#pragma unroll
+    for (int i = 0; i < 4; i++) out[i] = static_cast<float>(u.e[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; i++) out[i] = load_weight(p + i);
+  }
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void store_vec(T* p, const float (&in)[VEC])
+{
+  if constexpr (VEC == 4 && sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(in[0], in[1], in[2], in[3]);
+  } else if constexpr (VEC == 4 && sizeof(T) == 2) {
+    union {
+      uint2 raw;
+      T e[4];
+    } u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) u.e[i] = static_cast<T>(in[i]);
+    *reinterpret_cast<uint2*>(p) = u.raw;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; i++) store_weight(p + i, in[i]);
+  }
+}
+
+struct apply_params {
+  const uint32_t* keys;       // sorted local row ids
+  const int32_t* positions;   // list position of each sorted element
+  const int32_t* heads;
+  const int32_t* head_count;
+  int64_t n;
+  const float* grads;
+  int64_t grad_stride;
+  int dim;
+  void* weights;
+  int64_t weight_stride;
+  float* state;
+  int64_t state_stride;
+  int64_t v_offset;
+  float* beta12t;
+  optimizer_hyper h;
+};
+
+// One element of the update.  g is the summed gradient; w, s0, s1 are read-modify-write.
+template <int OPT>
+__device__ __forceinline__ void update_element(const optimizer_hyper& h, float g, float& w, float& s0,
+                                               float& s1, float beta1t, float beta2t)
+{
+  if (OPT == WHOLEGRAPH_OPT_SGD) {
+    g = __fadd_rn(g, __fmul_rn(h.weight_decay, w));
+    w = __fsub_rn(w, __fmul_rn(h.lr, g));
+  } else if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
+    if (h.adam_w) {
+      w = __fsub_rn(w, __fmul_rn(__fmul_rn(h.lr, h.weight_decay), w));
+    } else {
+      g = __fadd_rn(g, __fmul_rn(h.weight_decay, w));
+    }
+    float m = s0, v = s1;
+    m = __fadd_rn(__fmul_rn(h.beta1, m), __fmul_rn(__fsub_rn(1.f, h.beta1), g));
+    v = __fadd_rn(__fmul_rn(h.beta2, v), __fmul_rn(__fmul_rn(__fsub_rn(1.f, h.beta2), g), g));
+    const float mhat = __fdiv_rn(m, __fsub_rn(1.f, beta1t));
+    const float vhat = __fdiv_rn(v, __fsub_rn(1.f, beta2t));
+    w  = __fsub_rn(w, __fdiv_rn(__fmul_rn(h.lr, mhat), __fadd_rn(__fsqrt_rn(vhat), h.epsilon)));
+    s0 = m;
+    s1 = v;
+  } else if (OPT == WHOLEGRAPH_OPT_ADAGRAD) {
+    g  = __fadd_rn(g, __fmul_rn(h.weight_decay, w));
+    s0 = __fadd_rn(s0, __fmul_rn(g, g));
+    w  = __fsub_rn(w, __fdiv_rn(__fmul_rn(h.lr, g), __fadd_rn(__fsqrt_rn(s0), h.epsilon)));
+  } else {  // RMSProp
+    g  = __fadd_rn(g, __fmul_rn(h.weight_decay, w));
+    s0 = __fadd_rn(__fmul_rn(h.alpha, s0), __fmul_rn(__fmul_rn(__fsub_rn(1.f, h.alpha), g), g));
+    w  = __fsub_rn(w, __fdiv_rn(__fmul_rn(h.lr, g), __fadd_rn(__fsqrt_rn(s0), h.epsilon)));
+  }
+}
+
+// VEC = 4: dim, strides and base pointers allow float4 gradient / state accesses; VEC = 1 otherwise.
+template <int OPT, typename W, int VEC>
+__global__ void __launch_bounds__(kThreads) apply_kernel(const apply_params p)
+{
+  const int lane            = threadIdx.x & 31;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int runs            = *p.head_count;
+  W* weights                = static_cast<W*>(p.weights);
+
+  for (int64_t run = warp_global; run < runs; run += warp_stride) {
+    const int64_t first = p.heads[run];
+    const uint32_t row  = p.keys[first];
+    // length of the run: lanes probe 32 elements at a time
+    int64_t last = first + 1;
+    while (true) {
+      const int64_t probe = last + lane;
+      const bool same     = probe < p.n && p.keys[probe] == row;
+      const unsigned m    = __ballot_sync(0xffffffffu, same);
+      if (m == 0xffffffffu) {
+        last += 32;
+        continue;
+      }
+      last += __ffs(~m) - 1;
+      break;
+    }
+    float beta1t = 0.f, beta2t = 0.f;
+    if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
+      beta1t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 0], p.h.beta1);
+      beta2t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 1], p.h.beta2);
+    }
+    W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
+    float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
+
+    for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
+      float acc[VEC];
+      {
+        const float* g0 = p.grads + static_cast<int64_t>(p.positions[first]) * p.grad_stride + c;
+        if (VEC == 4) {
+          const float4 v = __ldg(reinterpret_cast<const float4*>(g0));
+          acc[0] = v.x, acc[1 % VEC] = v.y, acc[2 % VEC] = v.z, acc[3 % VEC] = v.w;
+        } else {
+          acc[0] = __ldg(g0);
+        }
+      }
+      // duplicates, in arrival order; four rows requested before the first is added
+      for (int64_t k = first + 1; k < last; k += 4) {
+        float v[4][VEC];
+        bool on[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          on[u] = k + u < last;
+          if (on[u]) {
+            const float* g = p.grads + static_cast<int64_t>(p.positions[k + u]) * p.grad_stride + c;
+            if (VEC == 4) {
+              const float4 t = __ldg(reinterpret_cast<const float4*>(g));
+              v[u][0] = t.x, v[u][1 % VEC] = t.y, v[u][2 % VEC] = t.z, v[u][3 % VEC] = t.w;
+            } else {
+              v[u][0] = __ldg(g);
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          if (on[u]) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
+          }
+        }
+      }
+      float w[VEC], s0[VEC], s1[VEC];
+      load_vec<W, VEC>(w_row + c, w);
+      if (OPT != WHOLEGRAPH_OPT_SGD) load_vec<float, VEC>(s_row + c, s0);
+      if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) load_vec<float, VEC>(s_row + p.v_offset + c, s1);
+#pragma unroll
+      for (int e = 0; e < VEC; e++) update_element<OPT>(p.h, acc[e], w[e], s0[e], s1[e], beta1t, beta2t);
+      if (OPT != WHOLEGRAPH_OPT_SGD) store_vec<float, VEC>(s_row + c, s0);
+      if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) store_vec<float, VEC>(s_row + p.v_offset + c, s1);
+      store_vec<W, VEC>(w_row + c, w);
+    }
+    if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM && lane == 0) {
+      p.beta12t[static_cast<int64_t>(row) * 2 + 0] = beta1t;
+      p.beta12t[static_cast<int64_t>(row) * 2 + 1] = beta2t;
+    }
+  }
+}
+
+__global__ void fill_kernel(float* data, float value, int64_t n)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) data[i] = value;
+}
+
+template <typename I>
+__global__ void round_robin_kernel(const I* ids, I* out, int64_t n, int world, int64_t entry_start, int rr)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const I id    = ids[i];
+  const I block = id / rr;
+  out[i]        = static_cast<I>(entry_start + static_cast<int64_t>(rr) * (block / world) + id % rr);
+}
+
+struct workspace_layout {
+  size_t keys_in, keys_out, pos_in, pos_out, heads, head_count, cub, total;
+  size_t cub_bytes;
+};
+
+int key_bits(int64_t local_rows)
+{
+  int bits = 1;
+  while (bits < 32 && (int64_t(1) << bits) <= local_rows) bits++;  // the sentinel is local_rows itself
+  return bits;
+}
+
+workspace_layout layout_for(int64_t n, int64_t local_rows)
+{
+  workspace_layout l{};
+  auto align = [](size_t x) { return (x + 255) / 256 * 256; };
+  const size_t cnt = static_cast<size_t>(std::max<int64_t>(n, 1));
+  size_t off       = 0;
+  l.keys_in        = off, off += align(cnt * 4);
+  l.keys_out       = off, off += align(cnt * 4);
+  l.pos_in         = off, off += align(cnt * 4);
+  l.pos_out        = off, off += align(cnt * 4);
+  l.heads          = off, off += align(cnt * 4);
+  l.head_count     = off, off += 256;
+  l.cub_bytes      = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, l.cub_bytes, static_cast<const uint32_t*>(nullptr),
+                                  static_cast<uint32_t*>(nullptr), static_cast<const int32_t*>(nullptr),
+                                  static_cast<int32_t*>(nullptr), static_cast<int>(cnt), 0,
+                                  key_bits(local_rows));
+  l.cub   = off, off += align(l.cub_bytes);
+  l.total = off;
+  return l;
+}
+
+template <int OPT, typename W>
+void launch_apply(const apply_params& p, bool vec4, int ctas, cudaStream_t stream)
+{
+  if (vec4)
+    apply_kernel<OPT, W, 4><<<ctas, kThreads, 0, stream>>>(p);
+  else
+    apply_kernel<OPT, W, 1><<<ctas, kThreads, 0, stream>>>(p);
+}
+
+template <typename W>
+void launch_apply_opt(const apply_params& p, bool vec4, int ctas, cudaStream_t stream)
+{
+  switch (p.h.type) {
+    case WHOLEGRAPH_OPT_SGD: launch_apply<WHOLEGRAPH_OPT_SGD, W>(p, vec4, ctas, stream); break;
+    case WHOLEGRAPH_OPT_LAZY_ADAM: launch_apply<WHOLEGRAPH_OPT_LAZY_ADAM, W>(p, vec4, ctas, stream); break;
+    case WHOLEGRAPH_OPT_ADAGRAD: launch_apply<WHOLEGRAPH_OPT_ADAGRAD, W>(p, vec4, ctas, stream); break;
+    case WHOLEGRAPH_OPT_RMSPROP: launch_apply<WHOLEGRAPH_OPT_RMSPROP, W>(p, vec4, ctas, stream); break;
+    default: WGB_EXPECTS(false, "unknown optimizer type %d", (int)p.h.type);
+  }
+}
+
+}  // namespace
+
+size_t sparse_apply_workspace_bytes(int64_t count, int64_t local_rows)
+{
+  return layout_for(count, local_rows).total;
+}
+
+void fill_float(float* data, float value, int64_t count, cudaStream_t stream)
+{
+  if (count <= 0) return;
+  fill_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(data, value, count);
+  count_kernel_launch();
+  WGB_LAUNCH_CHECK(stream);
+}
+
+void round_robin_remap(const void* ids, void* out, bool ids_are_64, int64_t count, int world,
+                       int64_t entry_start, int round_robin_size, cudaStream_t stream)
+{
+  if (count <= 0) return;
+  const unsigned blocks = static_cast<unsigned>((count + 255) / 256);
+  if (ids_are_64)
+    round_robin_kernel<int64_t><<<blocks, 256, 0, stream>>>(static_cast<const int64_t*>(ids),
+                                                            static_cast<int64_t*>(out), count, world,
+                                                            entry_start, round_robin_size);
+  else
+    round_robin_kernel<int><<<blocks, 256, 0, stream>>>(static_cast<const int*>(ids), static_cast<int*>(out),
+                                                        count, world, entry_start, round_robin_size);
+  count_kernel_launch();
+  WGB_LAUNCH_CHECK(stream);
+}
+
+void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stream)
+{
+  if (a.count == 0 || a.dim == 0) return;
+  WGB_EXPECTS(a.count < (int64_t(1) << 31), "gradient list of %ld rows is too long", (long)a.count);
+  WGB_EXPECTS(a.local_rows < (int64_t(1) << 32) - 1, "shard of %ld rows is too large", (long)a.local_rows);
+  WGB_EXPECTS(a.weight_dtype == WHOLEGRAPH_DT_FLOAT || a.weight_dtype == WHOLEGRAPH_DT_HALF ||
+                a.weight_dtype == WHOLEGRAPH_DT_BF16,
+              "only float, half and bf16 tables can be trained");
+  WGB_EXPECTS(a.hyper.type == WHOLEGRAPH_OPT_SGD || a.state != nullptr, "optimizer state is missing");
+  WGB_EXPECTS(a.hyper.type != WHOLEGRAPH_OPT_LAZY_ADAM || a.beta12t != nullptr, "beta12t is missing");
+  const workspace_layout l = layout_for(a.count, a.local_rows);
+  char* ws                 = static_cast<char*>(workspace);
+  auto* keys_in            = reinterpret_cast<uint32_t*>(ws + l.keys_in);
+  auto* keys_out           = reinterpret_cast<uint32_t*>(ws + l.keys_out);
+  auto* pos_in             = reinterpret_cast<int32_t*>(ws + l.pos_in);
+  auto* pos_out            = reinterpret_cast<int32_t*>(ws + l.pos_out);
+  auto* heads              = reinterpret_cast<int32_t*>(ws + l.heads);
+  auto* head_count         = reinterpret_cast<int32_t*>(ws + l.head_count);
+  const unsigned blocks    = static_cast<unsigned>((a.count + kThreads - 1) / kThreads);
+
+  keys_kernel<<<blocks, kThreads, 0, stream>>>(a.ids, a.ids_are_64 ? 1 : 0, a.count, a.local_start, a.local_rows,
+                                               keys_in, pos_in);
+  size_t cub_bytes = l.cub_bytes;
+  WGB_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(ws + l.cub, cub_bytes, keys_in, keys_out, pos_in, pos_out,
+                                                 static_cast<int>(a.count), 0, key_bits(a.local_rows),
+                                                 stream));
+  WGB_CUDA_CHECK(cudaMemsetAsync(head_count, 0, sizeof(int32_t), stream));
+  heads_kernel<<<blocks, kThreads, 0, stream>>>(keys_out, a.count, static_cast<uint32_t>(a.local_rows), heads,
+                                                head_count);
+
+  apply_params p;
+  p.keys = keys_out, p.positions = pos_out, p.heads = heads, p.head_count = head_count, p.n = a.count;
+  p.grads = a.grads, p.grad_stride = a.grad_stride, p.dim = static_cast<int>(a.dim);
+  p.weights = a.weights, p.weight_stride = a.weight_stride;
+  p.state = a.state, p.state_stride = a.state_stride, p.v_offset = a.v_offset, p.beta12t = a.beta12t;
+  p.h = a.hyper;
+  const size_t w_es = wholegraph_dtype_get_element_size(a.weight_dtype);
+  const bool vec4   = a.dim % 4 == 0 && a.grad_stride % 4 == 0 &&
+                    reinterpret_cast<uintptr_t>(a.grads) % 16 == 0 && a.weight_stride % 4 == 0 &&
+                    reinterpret_cast<uintptr_t>(a.weights) % (4 * w_es) == 0 &&
+                    (a.state == nullptr || (a.state_stride % 4 == 0 && a.v_offset % 4 == 0 &&
+                                            reinterpret_cast<uintptr_t>(a.state) % 16 == 0));
+  static int sm_count = [] {
+    int dev = 0, n = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  // One warp per distinct row, grid-stride; the number of rows is only known on the device.
+  const int64_t warps_wanted = a.count;
+  int ctas = static_cast<int>(std::min<int64_t>((warps_wanted + 7) / 8, static_cast<int64_t>(sm_count) * 8 * 4));
+  if (a.weight_dtype == WHOLEGRAPH_DT_FLOAT)
+    launch_apply_opt<float>(p, vec4, ctas, stream);
+  else if (a.weight_dtype == WHOLEGRAPH_DT_HALF)
+    launch_apply_opt<__half>(p, vec4, ctas, stream);
+  else
+    launch_apply_opt<__nv_bfloat16>(p, vec4, ctas, stream);
+  count_kernel_launch(4);
+  WGB_LAUNCH_CHECK(stream);
+}
+
+}  // namespace wgb

@@ -1,0 +1,69 @@
+// Host interface of the sparse optimizer: duplicate-gradient reduction fused with the update.
+// Replaces the reference's dedup_indice_and_gradients
+// (cpp/src/wholegraph_tensor_ops/functions/exchange_embeddings_nccl_func.cu:98-200) followed by
+// the per-row optimizer kernels (embedding_optimizer_func.cu:168-1022).
+#pragma once
+
+#include <cuda_runtime_api.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include <wholegraph/embedding.h>
+#include <wholegraph/tensor_description.h>
+
+namespace wgb {
+
+struct optimizer_hyper {
+  wholegraph_optimizer_type_t type = WHOLEGRAPH_OPT_NONE;
+  float lr           = 0.f;
+  float weight_decay = 0.f;
+  float epsilon      = 1e-8f;
+  float beta1        = 0.9f;
+  float beta2        = 0.999f;
+  float alpha        = 0.99f;
+  bool adam_w        = false;
+};
+
+struct sparse_apply_args {
+  // Gradient list as it arrived at the owner: ids[k] is a GLOBAL row id, its fp32 gradient row
+  // starts at grads + k * grad_stride.  Ids outside [local_start, local_start + local_rows) are
+  // ignored.
+  const void* ids      = nullptr;  // int32 or int64
+  bool ids_are_64      = true;
+  int64_t count        = 0;
+  const float* grads   = nullptr;
+  int64_t grad_stride  = 0;
+  int64_t dim          = 0;
+  // This rank's shard.
+  int64_t local_start  = 0;
+  int64_t local_rows   = 0;
+  void* weights        = nullptr;  // row r at weights + r * weight_stride elements
+  wholegraph_dtype_t weight_dtype = WHOLEGRAPH_DT_FLOAT;  // fp32 / fp16 / bf16
+  int64_t weight_stride = 0;
+  float* state         = nullptr;  // per-element fp32 state rows (m | v, state_sum, or v)
+  int64_t state_stride = 0;
+  int64_t v_offset     = 0;        // Lazy Adam: v lives v_offset elements after m in a state row
+  float* beta12t       = nullptr;  // Lazy Adam: [local_rows, 2] running beta1^t, beta2^t per row
+  optimizer_hyper hyper;
+};
+
+// Device scratch needed for a list of `count` gradient rows.
+size_t sparse_apply_workspace_bytes(int64_t count, int64_t local_rows);
+
+// Enqueue: group equal ids (stable radix sort of local row ids), add each group's gradient rows
+// one after the other in arrival order in fp32, and apply the optimizer to the row - all
+// without materialising the summed gradients.  Every product, sum, quotient and square root is
+// a separately rounded fp32 operation, in the order of the reference kernels.
+void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stream);
+
+// Fill `count` floats with `value` (state initialisation).
+void fill_float(float* data, float value, int64_t count, cudaStream_t stream);
+
+// Round-robin id remap, literal restatement of the reference's storage_idx2wg_emb_idx_kernel
+// (cpp/src/wholegraph_tensor_ops/functions/map_indices_func.cu:16-34):
+//   out[i] = entry_start + round_robin_size * ((ids[i] / round_robin_size) / world) + ids[i] % round_robin_size
+void round_robin_remap(const void* ids, void* out, bool ids_are_64, int64_t count, int world,
+                       int64_t entry_start, int round_robin_size, cudaStream_t stream);
+
+}  // namespace wgb

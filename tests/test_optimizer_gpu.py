@@ -1,0 +1,127 @@
+"""GPU parity of wholegraph_embedding_gather_gradient_apply (duplicate-gradient sum fused with
+SGD / Lazy Adam / AdaGrad / RMSProp) against the CPU oracle, through the C ABI.
+
+Grid after the reference's gradient-apply tests
+(cpp/tests/wholegraph_tensor_ops/wholegraph_embedding_gradient_apply_tests.cu:798-1007): four
+optimizers, dims 3/4/32/64/127/129/392, int32 and int64 ids, fp32 / fp16 / bf16 tables, several
+steps with duplicate ids.  The kernels round every operation separately in the oracle's order,
+so weights and states must match bit for bit (the required bound is 1e-6 relative)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+OPTS = {"sgd": 1, "adam": 2, "rmsprop": 3, "adagrad": 4}
+
+
+@pytest.fixture(scope="module")
+def comm(gpu, wgb):
+    c = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+    yield c
+    wgb.destroy_communicator(c)
+
+
+def _host_bits(torch, t):
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def _read_all(gpu, torch, wg_tensor, rows, dim, dtype):
+    ids = torch.arange(rows, device="cuda", dtype=torch.int64)
+    out = torch.empty((rows, dim), dtype=dtype, device="cuda")
+    gpu.gather(wg_tensor, ids, out)
+    torch.cuda.synchronize()
+    return out
+
+
+def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps, n, params, mem_type):
+    import torch
+    DT, MT, ML = wgb.WholeGraphDataType, wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[table_dtype]
+    wg_dt = gpu.TORCH_TO_WG[tdt]
+    rng = np.random.default_rng(hash((opt_name, dim, table_dtype)) % (2 ** 31))
+    env = wgb.cached_env_fns()
+    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(wg_dt)), comm, mem_type, ML.MlDevice)
+    opt = wgb.create_optimizer(wgb.WholeGraphOptimizerType(OPTS[opt_name]), **params)
+    wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
+    table = wgb.embedding_tensor(emb)
+
+    init = rng.uniform(-1, 1, size=(rows, dim)).astype(np.float32)
+    d_init = torch.from_numpy(init).cuda().to(tdt)
+    gpu.scatter(d_init, torch.arange(rows, device="cuda", dtype=torch.int64), table)
+    torch.cuda.synchronize()
+    # host mirrors
+    w_host = np.ascontiguousarray(_host_bits(torch, d_init))
+    padded = -(-dim // (16 // d_init.element_size())) * (16 // d_init.element_size())
+    n_states = {"sgd": 0, "adam": 2, "rmsprop": 1, "adagrad": 1}[opt_name]
+    state_host = np.zeros((rows, max(n_states, 1) * padded), dtype=np.float32)
+    beta_host = np.ones((rows, 2), dtype=np.float32)
+
+    lr = 0.01
+    for step in range(steps):
+        idx = rng.integers(0, rows, size=n)
+        idx[: n // 4] = idx[n // 2: n // 2 + n // 4]  # plenty of duplicates
+        idx = idx.astype(idx_dtype)
+        grads = rng.uniform(-1, 1, size=(n, dim)).astype(np.float32)
+        d_idx, d_grads = torch.from_numpy(idx).cuda(), torch.from_numpy(grads).cuda()  # keep them alive
+        wi, wg = gpu.wrap_torch_tensor(d_idx), gpu.wrap_torch_tensor(d_grads)
+        wgb.EmbeddingGatherGradientApply(emb, wi, wg, False, lr, env, gpu.current_stream_int())
+        torch.cuda.synchronize()
+        wgb.destroy_wholegraph_tensor(wi)
+        wgb.destroy_wholegraph_tensor(wg)
+        uniq, sums = orc.dedup_gradients(idx, grads)
+        orc.optimizer_apply(OPTS[opt_name], uniq, sums, w_host, lr=lr,
+                            state=state_host if n_states else None, v_offset=padded,
+                            beta12t=beta_host if opt_name == "adam" else None,
+                            weights_bf16=(table_dtype == "bf16"),
+                            weight_decay=params.get("weight_decay", 0.0), epsilon=params.get("epsilon", 1e-8),
+                            beta1=params.get("beta1", 0.9), beta2=params.get("beta2", 0.999),
+                            alpha=params.get("alpha", 0.99), adam_w=params.get("adam_w", 0.0) > 0.5)
+
+    got_w = _host_bits(torch, _read_all(gpu, torch, table, rows, dim, tdt))
+    assert np.array_equal(got_w.view(w_host.dtype), w_host), "weights differ from the oracle"
+    names = wgb.embedding_state_names(emb)
+    assert names == {"sgd": [], "adam": ["m", "v", "beta12t"], "rmsprop": ["v"], "adagrad": ["state_sum"]}[opt_name]
+    for k, name in enumerate([x for x in names if x != "beta12t"]):
+        st = _read_all(gpu, torch, wgb.embedding_state(emb, name), rows, dim, torch.float32).cpu().numpy()
+        assert np.array_equal(st, state_host[:, k * padded:k * padded + dim]), f"state {name} differs"
+    if opt_name == "adam":
+        b = _read_all(gpu, torch, wgb.embedding_state(emb, "beta12t"), rows, 2, torch.float32).cpu().numpy()
+        assert np.array_equal(b, beta_host)
+    wgb.destroy_embedding(emb)
+    wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
+
+
+@pytest.mark.parametrize("opt_name,params", [("sgd", {}), ("sgd", {"weight_decay": 0.1}),
+                                             ("adam", {}), ("adam", {"weight_decay": 0.05, "adam_w": 1.0}),
+                                             ("adam", {"weight_decay": 0.05, "beta1": 0.8, "epsilon": 1e-6}),
+                                             ("adagrad", {"weight_decay": 0.01}), ("rmsprop", {"alpha": 0.9})])
+@pytest.mark.parametrize("dim", [3, 4, 32, 64, 127, 129, 392])
+def test_gradient_apply_fp32(gpu, wgb, orc, comm, opt_name, params, dim):
+    _run(gpu, wgb, orc, comm, opt_name, 4096, dim, "f32", np.int64, 3, 3000, params,
+         wgb.WholeGraphMemoryType.MtDistributed)
+
+
+@pytest.mark.parametrize("opt_name", ["sgd", "adam", "adagrad", "rmsprop"])
+@pytest.mark.parametrize("table_dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
+def test_gradient_apply_half_tables(gpu, wgb, orc, comm, opt_name, table_dtype, idx_dtype):
+    _run(gpu, wgb, orc, comm, opt_name, 2048, 100, table_dtype, idx_dtype, 3, 1500, {},
+         wgb.WholeGraphMemoryType.MtContinuous)
+
+
+def test_gradient_apply_ten_steps_long_chains(gpu, wgb, orc, comm):
+    """Ten Lazy Adam steps on a small table so that every row is hit many times per step
+    (duplicate chains of ~40 rows), dim 256 as in the sparse-Adam configuration."""
+    _run(gpu, wgb, orc, comm, "adam", 256, 256, "f32", np.int64, 10, 10_000, {},
+         wgb.WholeGraphMemoryType.MtDistributed)
+
+
+def test_optimizer_parameter_names(gpu, wgb):
+    import ctypes as C
+    o = wgb.create_optimizer(wgb.WholeGraphOptimizerType.OptSgd)
+    v = C.c_float(0.5)
+    assert wgb.lib().wholegraph_optimizer_set_parameter(o, b"weight_decay", C.byref(v)) == 0
+    assert wgb.lib().wholegraph_optimizer_set_parameter(o, b"beta1", C.byref(v)) == int(wgb.ErrorCode.INVALID_INPUT)
+    wgb.lib().wholegraph_destroy_embedding_optimizer(o)
