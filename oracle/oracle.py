@@ -114,7 +114,7 @@ def gather(table: np.ndarray, indices: np.ndarray, out_dt: int | None = None, ou
         shape = (n,) if table.ndim == 1 else (n, dim)
         out = np.zeros(shape, dtype=np_dtype(out_dt))
     odim, ostride = _matrix_params(out)
-    assert odim == dim and out.shape[0] == n
+    assert odim == dim and (raw_pos is not None or out.shape[0] == n)
     indices = np.ascontiguousarray(indices)
     rp = None
     if raw_pos is not None:
