@@ -128,6 +128,66 @@ def main():
         wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
         wgb.destroy_wholegraph_tensor(t)
 
+    def check_gradient_apply(mem_type, opt_type, opt_code, rows, dim, n, steps, table_dtype=torch.float32):
+        print(f"rank {rank}: gradient apply {mem_type.name} opt={opt_code} rows={rows} dim={dim}", flush=True)
+        emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(tu.TORCH_TO_WG[table_dtype])), comm,
+                                   mem_type, ML.MlDevice)
+        opt = wgb.create_optimizer(opt_type, weight_decay=0.01)
+        wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
+        table = wgb.embedding_tensor(emb)
+        off = orc.equal_partition_offsets(rows, world)
+        lo, hi = int(off[rank]), int(off[rank + 1])
+        w0 = np.random.default_rng(5).uniform(-1, 1, size=(rows, dim)).astype(np.float32)
+        mine = torch.arange(lo, hi, device="cuda", dtype=torch.int64)
+        tu.scatter(torch.from_numpy(w0[lo:hi]).cuda().to(table_dtype), mine, table, env)
+        torch.cuda.synchronize()
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        w_host = np.ascontiguousarray(to_host(torch.from_numpy(w0).to(table_dtype)))
+        es = torch.empty((), dtype=table_dtype).element_size()
+        padded = -(-dim // (16 // es)) * (16 // es)
+        state = np.zeros((rows, 2 * padded), np.float32)
+        beta = np.ones((rows, 2), np.float32)
+        for step in range(steps):
+            all_ids, all_grads = [], []
+            for r in range(world):
+                rng = np.random.default_rng(1000 * step + r)
+                ids_r = rng.integers(0, rows, size=n).astype(np.int64)
+                ids_r[: n // 3] = ids_r[n // 3: 2 * (n // 3)]
+                all_ids.append(ids_r)
+                all_grads.append(rng.uniform(-1, 1, size=(n, dim)).astype(np.float32))
+            d_ids, d_grads = torch.from_numpy(all_ids[rank]).cuda(), torch.from_numpy(all_grads[rank]).cuda()
+            wi, wg = tu.wrap_torch_tensor(d_ids), tu.wrap_torch_tensor(d_grads)
+            wgb.EmbeddingGatherGradientApply(emb, wi, wg, False, 0.01, env, tu.current_stream_int())
+            torch.cuda.synchronize()
+            wgb.destroy_wholegraph_tensor(wi)
+            wgb.destroy_wholegraph_tensor(wg)
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            # oracle: duplicates summed in rank-then-arrival order, every row updated once
+            uniq, sums = orc.dedup_gradients(np.concatenate(all_ids), np.concatenate(all_grads))
+            orc.optimizer_apply(opt_code, uniq, sums, w_host, lr=0.01, state=state, v_offset=padded, beta12t=beta,
+                                weight_decay=0.01, weights_bf16=(table_dtype == torch.bfloat16))
+        got = torch.empty((hi - lo, dim), dtype=table_dtype, device="cuda")
+        tu.gather(table, mine, got, env)
+        torch.cuda.synchronize()
+        assert np.array_equal(to_host(got).view(w_host.dtype), w_host[lo:hi]), f"weights differ on rank {rank}"
+        for k, name in enumerate([x for x in wgb.embedding_state_names(emb) if x != "beta12t"]):
+            st = torch.empty((hi - lo, dim), dtype=torch.float32, device="cuda")
+            tu.gather(wgb.embedding_state(emb, name), mine, st, env)
+            torch.cuda.synchronize()
+            assert np.array_equal(st.cpu().numpy(), state[lo:hi, k * padded:k * padded + dim]), f"state {name} differs"
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        wgb.destroy_embedding(emb)
+        wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
+
+    if scenario == "optimizer":
+        OT = wgb.WholeGraphOptimizerType
+        check_gradient_apply(MT.MtDistributed, OT.OptLazyAdam, 2, 20_011, 64, 6_000, 3)
+        check_gradient_apply(MT.MtContinuous, OT.OptSgd, 1, 5_000, 33, 3_000, 2)
+        check_gradient_apply(MT.MtDistributed, OT.OptAdaGrad, 4, 8_000, 100, 3_000, 2, torch.float16)
+        check_gradient_apply(MT.MtDistributed, OT.OptRmsProp, 3, 3_000, 256, 9_000, 2, torch.bfloat16)
+        wgb.destroy_communicator(comm)
+        print(f"rank {rank} ok", flush=True)
+        return
     mem = {"continuous": MT.MtContinuous, "distributed": MT.MtDistributed, "chunked": MT.MtChunked}[scenario]
     check_gather(mem, 100_003, 128, torch.float16, torch.float16, 50_000, seed=1)
     check_gather(mem, 100_003, 128, torch.float32, torch.float16, 20_001, seed=2)
