@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "c2", "c3"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "c2", "c3", "c4", "c5"])
     ap.add_argument("--rows", type=int, default=0, help="override the table rows (profiling on a small case)")
     ap.add_argument("--ids", type=int, default=0, help="override the ids per rank")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -181,6 +181,96 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_sparse_adam(args, torch, dist, wgb, tu, comm, world, rank, local_rank):
+    """C5: one Lazy Adam step per bench step on a DISTRIBUTED fp32 table of dim 256; every rank
+    feeds 2,097,152 fp32 gradient rows at Zipf(1.1) ids; duplicates are summed before the update."""
+    import ctypes as C
+    dim, multi = 256, world > 1
+    rows = args.rows or (50_000_000 if world == 8 else 6_250_000 * world)   # 6.25 M rows per GPU
+    n = args.ids or 2_097_152
+    DT, MT, ML = wgb.WholeGraphDataType, wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation
+    env = wgb.cached_env_fns()
+    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT.DtFloat), comm, MT.MtDistributed, ML.MlDevice)
+    opt = wgb.create_optimizer(wgb.WholeGraphOptimizerType.OptLazyAdam)
+    wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
+    table = wgb.embedding_tensor(emb)
+    local_rows = C.c_size_t()
+    wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_count(C.byref(local_rows), table), "entry_count")
+    gen = torch.Generator(device="cuda").manual_seed(rank)
+    for s in range(0, local_rows.value, 2_000_000):
+        piece = torch.empty((min(2_000_000, local_rows.value - s), dim), dtype=torch.float32, device="cuda")
+        piece.normal_(0, 0.01, generator=gen)
+        tu.write_local_shard(table, piece, s)
+    perm = torch.randperm(rows, generator=torch.Generator(device="cuda").manual_seed(7), device="cuda")
+    batches = []
+    for b in range(2):
+        g = torch.Generator(device="cuda").manual_seed(1000 * b + rank)
+        ids = zipf_ids(torch, n, rows, 1.1, perm, g)
+        grads = torch.empty((n, dim), dtype=torch.float32, device="cuda").normal_(0, 1e-3, generator=g)
+        batches.append((ids, grads, tu.wrap_torch_tensor(ids), tu.wrap_torch_tensor(grads)))
+    del perm
+    unique_global = int(torch.unique(batches[0][0]).numel())
+    stream = tu.current_stream_int()
+
+    def step(i):
+        _, _, wi, wg = batches[i % 2]
+        wgb.EmbeddingGatherGradientApply(emb, wi, wg, False, 1e-3, env, stream)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if multi:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = wgb.lib().wholegraph_b200_kernel_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    launches = wgb.lib().wholegraph_b200_kernel_launch_count() - l0
+    ms = e0.elapsed_time(e1)
+    if multi:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        peak, how = measured_hbm_peak()
+        # per rank: every raw gradient row read once (1024 B) + 7184 B per distinct row it owns
+        alg = n * dim * 4 + (unique_global / world) * 7184 if not multi else n * dim * 4 + unique_global * 7184
+        achieved = alg / (ms_step * 1e-3) / 1e9
+        line = {"metric": "sparse-Adam rows/s", "value": world * n / (ms_step * 1e-3), "unit": "rows/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": f"C5: Lazy Adam on a {rows} x {dim} fp32 DISTRIBUTED table over {world} GPUs, "
+                                       f"{n} gradient rows N(0,1e-3) per rank per step at Zipf(1.1) ids, lr 1e-3",
+                           "distinct_ids_rank0_batch0": unique_global},
+                "gpu_launches": int(launches), "clocks": clocks,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                             "traffic": None, "peak_source": how,
+                             "note": "1024 B per raw gradient row + 7184 B per distinct updated row (single-rank estimate "
+                                     "from rank 0's first batch)"}}
+        print(json.dumps(line), flush=True)
+    for _, _, wi, wg in batches:
+        wgb.destroy_wholegraph_tensor(wi)
+        wgb.destroy_wholegraph_tensor(wg)
+    barrier()
+    wgb.destroy_embedding(emb)
+    wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
+    wgb.destroy_communicator(comm)
+    if multi:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -220,22 +310,35 @@ def main():
     else:
         comm = wgb.create_communicator(wgb.UniqueId(), 0, 1)
 
-    n_ids = args.ids or IDS_PER_RANK
+    if workload == "c5":
+        run_sparse_adam(args, torch, dist, wgb, tu, comm, world, rank, local_rank)
+        return
+    MT = wgb.WholeGraphMemoryType
+    mem_type, zipf_alpha = MT.MtContinuous, None
     if workload == "c2":
+        n_ids = args.ids or IDS_PER_RANK
         rows = args.rows or 10_000_000
         tab_dtype, out_dtype, tab_wg = torch.float32, torch.float16, wgb.WholeGraphDataType.DtFloat
         name = f"C2: {rows} x {ROW_DIM} fp32 CONTINUOUS/DEVICE table, {n_ids} int64 ids uniform with replacement, gather with cast to fp16"
-    else:
+    elif workload == "c3":
+        n_ids = args.ids or IDS_PER_RANK
         rows = args.rows or 100_000_000
+        zipf_alpha = 1.1
         tab_dtype, out_dtype, tab_wg = torch.float16, torch.float16, wgb.WholeGraphDataType.DtHalf
         name = (f"C3: {rows} x {ROW_DIM} fp16 table row-sharded CONTINUOUS/DEVICE over {world} GPUs, "
                 f"{n_ids} int64 Zipf(1.1) ids per rank over a seeded permutation, fp16 output")
+    else:
+        n_ids = args.ids or 4_194_304
+        rows = args.rows or 240_000_000
+        zipf_alpha, mem_type = 1.2, MT.MtDistributed
+        tab_dtype, out_dtype, tab_wg = torch.bfloat16, torch.bfloat16, wgb.WholeGraphDataType.DtBF16
+        name = (f"C4: {rows} x {ROW_DIM} bf16 table row-sharded DISTRIBUTED (NCCL exchange) over {world} GPUs, "
+                f"{n_ids} int64 Zipf(1.2) ids per rank over a seeded permutation, bf16 output")
     es_tab = torch.empty((), dtype=tab_dtype).element_size()
     es_out = torch.empty((), dtype=out_dtype).element_size()
 
     desc = wgb.make_description([rows, ROW_DIM], tab_wg)
-    table = wgb.create_wholegraph_tensor(desc, comm, wgb.WholeGraphMemoryType.MtContinuous,
-                                         wgb.WholeGraphMemoryLocation.MlDevice)
+    table = wgb.create_wholegraph_tensor(desc, comm, mem_type, wgb.WholeGraphMemoryLocation.MlDevice)
     local_rows = wgb.C.c_size_t()
     wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_count(wgb.C.byref(local_rows), table), "entry_count")
     local_rows = local_rows.value
@@ -257,7 +360,7 @@ def main():
         perm = torch.randperm(rows, generator=torch.Generator(device="cuda").manual_seed(7), device="cuda")
         for b in range(INDEX_BATCHES):
             g = torch.Generator(device="cuda").manual_seed(100 + rank + 1000 * b)
-            batches.append(zipf_ids(torch, n_ids, rows, 1.1, perm, g))
+            batches.append(zipf_ids(torch, n_ids, rows, zipf_alpha, perm, g))
         del perm
         torch.cuda.empty_cache()
     out = torch.empty((n_ids, ROW_DIM), dtype=out_dtype, device="cuda")
@@ -333,12 +436,20 @@ def main():
     # ---- roofline of the copy kernel -------------------------------------------------------
     algorithmic = n_ids * (ROW_DIM * es_tab + ROW_DIM * es_out + 8)   # row read + row write + id read
     if multi:
-        ingress = n_ids * ROW_DIM * es_tab * (world - 1) / world
+        per = -(-rows // world)
+        b0 = batches[0]
+        remote = b0[(b0 // per) != rank]
+        remote_ids, remote_unique = int(remote.numel()), int(torch.unique(remote).numel())
+        wire_row = ROW_DIM * (es_out if workload == "c4" else es_tab)   # DISTRIBUTED casts at the owner
+        ingress = remote_ids * wire_row
         achieved = ingress / (ms_step * 1e-3) / 1e9
         roofline = {"bound": "nvlink", "achieved": achieved, "peak": NVLINK_PEER_GBS, "unit": "GB/s",
                     "frac": achieved / NVLINK_PEER_GBS, "traffic": None,
-                    "note": "NVLink ingress bytes per rank per launch ((W-1)/W of the row reads) over the "
-                            "measured 770 GB/s peer copy; uniform-owner estimate, of measured"}
+                    "remote_ids": remote_ids, "remote_unique_ids": remote_unique,
+                    "note": "NVLink ingress per rank per step = ids owned by other ranks x row bytes (rank 0, "
+                            "batch 0), no credit for repeated ids, over the measured 770 GB/s peer copy (of "
+                            "measured); on mapped memory repeated remote rows are served by caches, so a "
+                            "skewed request list can exceed 1"}
     else:
         peak, how = measured_hbm_peak()
         achieved = algorithmic / (ms_step * 1e-3) / 1e9
@@ -369,9 +480,9 @@ def main():
             "metric": "gathered embedding GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32->f16" if workload == "c2" else "f16", "data": "synthetic",
+            "dtype": {"c2": "f32->f16", "c3": "f16", "c4": "bf16"}[workload], "data": "synthetic",
             "config": {"workload": name, "l2": "table and output larger than L2; a different index batch each step",
-                       "memory_type": "CONTINUOUS/DEVICE", "ids_per_rank": n_ids, "rows": rows, "dim": ROW_DIM},
+                       "memory_type": ("DISTRIBUTED" if workload == "c4" else "CONTINUOUS") + "/DEVICE", "ids_per_rank": n_ids, "rows": rows, "dim": ROW_DIM},
             "gpu_launches": int(launches), "roofline": roofline, "clocks": clocks,
         }
         if e2e is not None:

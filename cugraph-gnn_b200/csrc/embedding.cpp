@@ -202,7 +202,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     if (n == 0) return;
     a.ids = ids, a.ids_are_64 = ids_are_64, a.count = n;
     a.grads = g, a.grad_stride = gd->strides[0];
-    sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(n, wl.rows)), stream);
+    sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(n, wl.rows, e->dim)), stream);
     return;
   }
 
@@ -246,7 +246,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   if (plan.total_recv == 0) return;
   a.ids = plan.recv_ids, a.ids_are_64 = true, a.count = plan.total_recv;
   a.grads = reinterpret_cast<const float*>(recv), a.grad_stride = e->dim;
-  sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(plan.total_recv, wl.rows)), stream);
+  sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(plan.total_recv, wl.rows, e->dim)), stream);
 }
 
 // Run `fn(mapped indices)`, remapping the ids first when the embedding is sharded round-robin.

@@ -28,7 +28,8 @@ namespace wgb {
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads    = 256;
+constexpr int kDedupBlock = WHOLEGRAPH_B200_DEDUP_BLOCK;  // rows per block of a long duplicate run
 
 __global__ void keys_kernel(const void* ids, int is64, int64_t n, int64_t local_start,
                             int64_t local_rows, uint32_t* keys, int32_t* positions)
@@ -127,6 +128,15 @@ struct apply_params {
   int64_t v_offset;
   float* beta12t;
   optimizer_hyper h;
+  // Runs longer than kDedupBlock rows are summed in blocks (see sum_blocks_kernel).
+  int32_t* long_first;    // per long run: index of its first sorted element
+  int32_t* long_len;      // per long run: number of elements
+  int32_t* long_slot;     // per long run: first partial-sum slot
+  int32_t* long_count;    // number of long runs
+  int32_t* slot_count;    // number of partial-sum slots handed out
+  int32_t* slot_run;      // per slot: long run it belongs to
+  int32_t* slot_block;    // per slot: block number inside the run
+  float* partial;         // [slots, dim] block sums
 };
 
 // One element of the update.  g is the summed gradient; w, s0, s1 are read-modify-write.
@@ -162,7 +172,83 @@ __device__ __forceinline__ void update_element(const optimizer_hyper& h, float g
   }
 }
 
-// VEC = 4: dim, strides and base pointers allow float4 gradient / state accesses; VEC = 1 otherwise.
+// Sum of the gradient rows of sorted elements [first, last) for columns [c, c + VEC), added one
+// after the other in that order; four rows are requested before the first is added.
+template <int VEC>
+__device__ __forceinline__ void sum_rows(const apply_params& p, int64_t first, int64_t last, int c,
+                                         float (&acc)[VEC])
+{
+  {
+    const float* g0 = p.grads + static_cast<int64_t>(p.positions[first]) * p.grad_stride + c;
+    if constexpr (VEC == 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(g0));
+      acc[0] = v.x, acc[1] = v.y, acc[2] = v.z, acc[3] = v.w;
+    } else {
+      acc[0] = __ldg(g0);
+    }
+  }
+  for (int64_t k = first + 1; k < last; k += 4) {
+    float v[4][VEC];
+    bool on[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      on[u] = k + u < last;
+      if (on[u]) {
+        const float* g = p.grads + static_cast<int64_t>(p.positions[k + u]) * p.grad_stride + c;
+        if constexpr (VEC == 4) {
+          const float4 t = __ldg(reinterpret_cast<const float4*>(g));
+          v[u][0] = t.x, v[u][1] = t.y, v[u][2] = t.z, v[u][3] = t.w;
+        } else {
+          v[u][0] = __ldg(g);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      if (on[u]) {
+#pragma unroll
+        for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
+      }
+    }
+  }
+}
+
+// Read-modify-write of weights and state for columns [c, c + VEC) of one row.
+template <int OPT, typename W, int VEC>
+__device__ __forceinline__ void update_columns(const apply_params& p, W* w_row, float* s_row, int c,
+                                               const float (&acc)[VEC], float beta1t, float beta2t)
+{
+  float w[VEC], s0[VEC], s1[VEC];
+  load_vec<W, VEC>(w_row + c, w);
+  if (OPT != WHOLEGRAPH_OPT_SGD) load_vec<float, VEC>(s_row + c, s0);
+  if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) load_vec<float, VEC>(s_row + p.v_offset + c, s1);
+#pragma unroll
+  for (int e = 0; e < VEC; e++) update_element<OPT>(p.h, acc[e], w[e], s0[e], s1[e], beta1t, beta2t);
+  if (OPT != WHOLEGRAPH_OPT_SGD) store_vec<float, VEC>(s_row + c, s0);
+  if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) store_vec<float, VEC>(s_row + p.v_offset + c, s1);
+  store_vec<W, VEC>(w_row + c, w);
+}
+
+// Per-row running beta1^t, beta2^t of Lazy Adam: multiplied on every touch of the row.
+template <int OPT>
+__device__ __forceinline__ void step_betas(const apply_params& p, uint32_t row, int lane, float& beta1t,
+                                           float& beta2t)
+{
+  beta1t = beta2t = 0.f;
+  if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
+    beta1t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 0], p.h.beta1);
+    beta2t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 1], p.h.beta2);
+    __syncwarp();  // every lane has read the old values before lane 0 overwrites them
+    if (lane == 0) {
+      p.beta12t[static_cast<int64_t>(row) * 2 + 0] = beta1t;
+      p.beta12t[static_cast<int64_t>(row) * 2 + 1] = beta2t;
+    }
+  }
+}
+
+// One warp per distinct row.  Runs of up to kDedupBlock duplicates are summed and applied here;
+// longer runs are only registered, with one partial-sum slot per block of kDedupBlock rows.
+// VEC = 4: dim, strides and base pointers allow 16-byte accesses; VEC = 1 otherwise.
 template <int OPT, typename W, int VEC>
 __global__ void __launch_bounds__(kThreads) apply_kernel(const apply_params p)
 {
@@ -188,63 +274,88 @@ __global__ void __launch_bounds__(kThreads) apply_kernel(const apply_params p)
       last += __ffs(~m) - 1;
       break;
     }
-    float beta1t = 0.f, beta2t = 0.f;
-    if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
-      beta1t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 0], p.h.beta1);
-      beta2t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 1], p.h.beta2);
+    const int64_t len = last - first;
+    if (len > kDedupBlock) {
+      const int blocks = static_cast<int>((len + kDedupBlock - 1) / kDedupBlock);
+      int li = 0, slot = 0;
+      if (lane == 0) {
+        li               = atomicAdd(p.long_count, 1);
+        slot             = atomicAdd(p.slot_count, blocks);
+        p.long_first[li] = static_cast<int32_t>(first);
+        p.long_len[li]   = static_cast<int32_t>(len);
+        p.long_slot[li]  = slot;
+      }
+      li   = __shfl_sync(0xffffffffu, li, 0);
+      slot = __shfl_sync(0xffffffffu, slot, 0);
+      for (int b = lane; b < blocks; b += 32) {
+        p.slot_run[slot + b]   = li;
+        p.slot_block[slot + b] = b;
+      }
+      continue;
     }
+    float beta1t, beta2t;
+    step_betas<OPT>(p, row, lane, beta1t, beta2t);
     W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
     float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
-
     for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
       float acc[VEC];
-      {
-        const float* g0 = p.grads + static_cast<int64_t>(p.positions[first]) * p.grad_stride + c;
-        if (VEC == 4) {
-          const float4 v = __ldg(reinterpret_cast<const float4*>(g0));
-          acc[0] = v.x, acc[1 % VEC] = v.y, acc[2 % VEC] = v.z, acc[3 % VEC] = v.w;
-        } else {
-          acc[0] = __ldg(g0);
-        }
-      }
-      // duplicates, in arrival order; four rows requested before the first is added
-      for (int64_t k = first + 1; k < last; k += 4) {
-        float v[4][VEC];
-        bool on[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          on[u] = k + u < last;
-          if (on[u]) {
-            const float* g = p.grads + static_cast<int64_t>(p.positions[k + u]) * p.grad_stride + c;
-            if (VEC == 4) {
-              const float4 t = __ldg(reinterpret_cast<const float4*>(g));
-              v[u][0] = t.x, v[u][1 % VEC] = t.y, v[u][2 % VEC] = t.z, v[u][3 % VEC] = t.w;
-            } else {
-              v[u][0] = __ldg(g);
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          if (on[u]) {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
-          }
-        }
-      }
-      float w[VEC], s0[VEC], s1[VEC];
-      load_vec<W, VEC>(w_row + c, w);
-      if (OPT != WHOLEGRAPH_OPT_SGD) load_vec<float, VEC>(s_row + c, s0);
-      if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) load_vec<float, VEC>(s_row + p.v_offset + c, s1);
-#pragma unroll
-      for (int e = 0; e < VEC; e++) update_element<OPT>(p.h, acc[e], w[e], s0[e], s1[e], beta1t, beta2t);
-      if (OPT != WHOLEGRAPH_OPT_SGD) store_vec<float, VEC>(s_row + c, s0);
-      if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) store_vec<float, VEC>(s_row + p.v_offset + c, s1);
-      store_vec<W, VEC>(w_row + c, w);
+      sum_rows<VEC>(p, first, last, c, acc);
+      update_columns<OPT, W, VEC>(p, w_row, s_row, c, acc, beta1t, beta2t);
     }
-    if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM && lane == 0) {
-      p.beta12t[static_cast<int64_t>(row) * 2 + 0] = beta1t;
-      p.beta12t[static_cast<int64_t>(row) * 2 + 1] = beta2t;
+  }
+}
+
+// One warp per partial-sum slot: block b of a long run, rows [b * kDedupBlock, (b + 1) * kDedupBlock)
+// of the run, added in order.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) sum_blocks_kernel(const apply_params p)
+{
+  const int lane            = threadIdx.x & 31;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int slots           = *p.slot_count;
+  for (int64_t s = warp_global; s < slots; s += warp_stride) {
+    const int li        = p.slot_run[s];
+    const int64_t begin = p.long_first[li];
+    const int64_t end   = begin + p.long_len[li];
+    const int64_t first = begin + static_cast<int64_t>(p.slot_block[s]) * kDedupBlock;
+    const int64_t last  = first + kDedupBlock < end ? first + kDedupBlock : end;
+    float* out          = p.partial + s * p.dim;
+    for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
+      float acc[VEC];
+      sum_rows<VEC>(p, first, last, c, acc);
+#pragma unroll
+      for (int e = 0; e < VEC; e++) out[c + e] = acc[e];
+    }
+  }
+}
+
+// One warp per long run: adds its block sums in block order and applies the optimizer.
+template <int OPT, typename W, int VEC>
+__global__ void __launch_bounds__(kThreads) apply_long_kernel(const apply_params p)
+{
+  const int lane            = threadIdx.x & 31;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int runs            = *p.long_count;
+  W* weights                = static_cast<W*>(p.weights);
+  for (int64_t li = warp_global; li < runs; li += warp_stride) {
+    const uint32_t row = p.keys[p.long_first[li]];
+    const int blocks   = (p.long_len[li] + kDedupBlock - 1) / kDedupBlock;
+    const float* part  = p.partial + static_cast<int64_t>(p.long_slot[li]) * p.dim;
+    float beta1t, beta2t;
+    step_betas<OPT>(p, row, lane, beta1t, beta2t);
+    W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
+    float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
+    for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
+      float acc[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; e++) acc[e] = part[c + e];
+      for (int b = 1; b < blocks; b++) {
+#pragma unroll
+        for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], part[static_cast<int64_t>(b) * p.dim + c + e]);
+      }
+      update_columns<OPT, W, VEC>(p, w_row, s_row, c, acc, beta1t, beta2t);
     }
   }
 }
@@ -266,7 +377,8 @@ __global__ void round_robin_kernel(const I* ids, I* out, int64_t n, int world, i
 }
 
 struct workspace_layout {
-  size_t keys_in, keys_out, pos_in, pos_out, heads, head_count, cub, total;
+  size_t keys_in, keys_out, pos_in, pos_out, heads, counters, cub, total;
+  size_t long_first, long_len, long_slot, slot_run, slot_block, partial;
   size_t cub_bytes;
 };
 
@@ -277,7 +389,7 @@ int key_bits(int64_t local_rows)
   return bits;
 }
 
-workspace_layout layout_for(int64_t n, int64_t local_rows)
+workspace_layout layout_for(int64_t n, int64_t local_rows, int64_t dim)
 {
   workspace_layout l{};
   auto align = [](size_t x) { return (x + 255) / 256 * 256; };
@@ -288,7 +400,16 @@ workspace_layout layout_for(int64_t n, int64_t local_rows)
   l.pos_in         = off, off += align(cnt * 4);
   l.pos_out        = off, off += align(cnt * 4);
   l.heads          = off, off += align(cnt * 4);
-  l.head_count     = off, off += 256;
+  l.counters       = off, off += 256;  // head count, long-run count, slot count
+  // At most n / block runs are long, and they need at most n / block + (their number) slots.
+  const size_t max_long  = cnt / kDedupBlock + 1;
+  const size_t max_slots = 2 * max_long;
+  l.long_first = off, off += align(max_long * 4);
+  l.long_len   = off, off += align(max_long * 4);
+  l.long_slot  = off, off += align(max_long * 4);
+  l.slot_run   = off, off += align(max_slots * 4);
+  l.slot_block = off, off += align(max_slots * 4);
+  l.partial    = off, off += align(max_slots * static_cast<size_t>(std::max<int64_t>(dim, 1)) * 4);
   l.cub_bytes      = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, l.cub_bytes, static_cast<const uint32_t*>(nullptr),
                                   static_cast<uint32_t*>(nullptr), static_cast<const int32_t*>(nullptr),
@@ -302,10 +423,17 @@ workspace_layout layout_for(int64_t n, int64_t local_rows)
 template <int OPT, typename W>
 void launch_apply(const apply_params& p, bool vec4, int ctas, cudaStream_t stream)
 {
-  if (vec4)
+  // Long runs are rare and their number is only known on the device: fixed modest grids.
+  const int long_ctas = std::min(ctas, 148 * 4);
+  if (vec4) {
     apply_kernel<OPT, W, 4><<<ctas, kThreads, 0, stream>>>(p);
-  else
+    sum_blocks_kernel<4><<<long_ctas, kThreads, 0, stream>>>(p);
+    apply_long_kernel<OPT, W, 4><<<long_ctas, kThreads, 0, stream>>>(p);
+  } else {
     apply_kernel<OPT, W, 1><<<ctas, kThreads, 0, stream>>>(p);
+    sum_blocks_kernel<1><<<long_ctas, kThreads, 0, stream>>>(p);
+    apply_long_kernel<OPT, W, 1><<<long_ctas, kThreads, 0, stream>>>(p);
+  }
 }
 
 template <typename W>
@@ -322,9 +450,9 @@ void launch_apply_opt(const apply_params& p, bool vec4, int ctas, cudaStream_t s
 
 }  // namespace
 
-size_t sparse_apply_workspace_bytes(int64_t count, int64_t local_rows)
+size_t sparse_apply_workspace_bytes(int64_t count, int64_t local_rows, int64_t dim)
 {
-  return layout_for(count, local_rows).total;
+  return layout_for(count, local_rows, dim).total;
 }
 
 void fill_float(float* data, float value, int64_t count, cudaStream_t stream)
@@ -361,14 +489,15 @@ void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stre
               "only float, half and bf16 tables can be trained");
   WGB_EXPECTS(a.hyper.type == WHOLEGRAPH_OPT_SGD || a.state != nullptr, "optimizer state is missing");
   WGB_EXPECTS(a.hyper.type != WHOLEGRAPH_OPT_LAZY_ADAM || a.beta12t != nullptr, "beta12t is missing");
-  const workspace_layout l = layout_for(a.count, a.local_rows);
+  const workspace_layout l = layout_for(a.count, a.local_rows, a.dim);
   char* ws                 = static_cast<char*>(workspace);
   auto* keys_in            = reinterpret_cast<uint32_t*>(ws + l.keys_in);
   auto* keys_out           = reinterpret_cast<uint32_t*>(ws + l.keys_out);
   auto* pos_in             = reinterpret_cast<int32_t*>(ws + l.pos_in);
   auto* pos_out            = reinterpret_cast<int32_t*>(ws + l.pos_out);
   auto* heads              = reinterpret_cast<int32_t*>(ws + l.heads);
-  auto* head_count         = reinterpret_cast<int32_t*>(ws + l.head_count);
+  auto* counters           = reinterpret_cast<int32_t*>(ws + l.counters);
+  auto* head_count         = counters;
   const unsigned blocks    = static_cast<unsigned>((a.count + kThreads - 1) / kThreads);
 
   keys_kernel<<<blocks, kThreads, 0, stream>>>(a.ids, a.ids_are_64 ? 1 : 0, a.count, a.local_start, a.local_rows,
@@ -377,7 +506,7 @@ void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stre
   WGB_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(ws + l.cub, cub_bytes, keys_in, keys_out, pos_in, pos_out,
                                                  static_cast<int>(a.count), 0, key_bits(a.local_rows),
                                                  stream));
-  WGB_CUDA_CHECK(cudaMemsetAsync(head_count, 0, sizeof(int32_t), stream));
+  WGB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 3 * sizeof(int32_t), stream));
   heads_kernel<<<blocks, kThreads, 0, stream>>>(keys_out, a.count, static_cast<uint32_t>(a.local_rows), heads,
                                                 head_count);
 
@@ -387,6 +516,13 @@ void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stre
   p.weights = a.weights, p.weight_stride = a.weight_stride;
   p.state = a.state, p.state_stride = a.state_stride, p.v_offset = a.v_offset, p.beta12t = a.beta12t;
   p.h = a.hyper;
+  p.long_count = counters + 1, p.slot_count = counters + 2;
+  p.long_first = reinterpret_cast<int32_t*>(ws + l.long_first);
+  p.long_len   = reinterpret_cast<int32_t*>(ws + l.long_len);
+  p.long_slot  = reinterpret_cast<int32_t*>(ws + l.long_slot);
+  p.slot_run   = reinterpret_cast<int32_t*>(ws + l.slot_run);
+  p.slot_block = reinterpret_cast<int32_t*>(ws + l.slot_block);
+  p.partial    = reinterpret_cast<float*>(ws + l.partial);
   const size_t w_es = wholegraph_dtype_get_element_size(a.weight_dtype);
   const bool vec4   = a.dim % 4 == 0 && a.grad_stride % 4 == 0 &&
                     reinterpret_cast<uintptr_t>(a.grads) % 16 == 0 && a.weight_stride % 4 == 0 &&
@@ -408,7 +544,7 @@ void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stre
     launch_apply_opt<__half>(p, vec4, ctas, stream);
   else
     launch_apply_opt<__nv_bfloat16>(p, vec4, ctas, stream);
-  count_kernel_launch(4);
+  count_kernel_launch(6);
   WGB_LAUNCH_CHECK(stream);
 }
 

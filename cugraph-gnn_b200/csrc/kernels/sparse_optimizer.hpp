@@ -10,6 +10,7 @@
 #include <cstdint>
 
 #include <wholegraph/embedding.h>
+#include <wholegraph/wholegraph_b200.h>
 #include <wholegraph/tensor_description.h>
 
 namespace wgb {
@@ -49,11 +50,14 @@ struct sparse_apply_args {
 };
 
 // Device scratch needed for a list of `count` gradient rows.
-size_t sparse_apply_workspace_bytes(int64_t count, int64_t local_rows);
+size_t sparse_apply_workspace_bytes(int64_t count, int64_t local_rows, int64_t dim);
 
 // Enqueue: group equal ids (stable radix sort of local row ids), add each group's gradient rows
-// one after the other in arrival order in fp32, and apply the optimizer to the row - all
-// without materialising the summed gradients.  Every product, sum, quotient and square root is
+// one after the other in arrival order in fp32, and apply the optimizer to the row - without
+// materialising the summed gradients.  A group of more than WHOLEGRAPH_B200_DEDUP_BLOCK rows is
+// cut into blocks of that many rows (in arrival order); each block is summed in order, and the
+// block sums are then added in block order.  That is the one place where the order of additions
+// differs from the reference's single chain; it keeps a hot row from serialising the step.  Every product, sum, quotient and square root is
 // a separately rounded fp32 operation, in the order of the reference kernels.
 void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stream);
 

@@ -11,6 +11,14 @@
 #include <wholegraph/env_func_ptrs.h>
 #include <wholegraph/wholegraph.h>
 
+/*
+ * Duplicate-gradient reduction of wholegraph_embedding_gather_gradient_apply: gradients of equal
+ * ids are added one after the other in arrival order, as in the reference, as long as an id
+ * occurs at most this many times in one call.  Longer runs are cut into blocks of this many
+ * rows; each block is summed in order and the block sums are added in block order.
+ */
+#define WHOLEGRAPH_B200_DEDUP_BLOCK 256
+
 #ifdef __cplusplus
 extern "C" {
 #endif

@@ -56,8 +56,8 @@ def lib() -> C.CDLL:
         _lib.wgo_owner.argtypes = [i64, vp, ci]
         _lib.wgo_bucket_sort_ids.restype = ci
         _lib.wgo_bucket_sort_ids.argtypes = [vp, ci, i64, vp, ci, vp, vp, vp]
-        _lib.wgo_dedup_gradients.restype = i64
-        _lib.wgo_dedup_gradients.argtypes = [vp, ci, i64, vp, ci, i64, i64, vp, vp]
+        _lib.wgo_dedup_gradients_blocked.restype = i64
+        _lib.wgo_dedup_gradients_blocked.argtypes = [vp, ci, i64, vp, ci, i64, i64, i64, vp, vp]
         _lib.wgo_optimizer_apply.restype = ci
         _lib.wgo_optimizer_apply.argtypes = [ci, vp, i64, vp, i64, i64, vp, ci, i64, vp, i64, i64, vp, i64,
                                              C.c_float, C.c_float, C.c_float, C.c_float, C.c_float,
@@ -162,15 +162,16 @@ def bucket_sort_ids(indices: np.ndarray, offsets: np.ndarray):
     return counts, sorted_ids, raw_pos
 
 
-def dedup_gradients(indices: np.ndarray, grads: np.ndarray, grads_bf16: bool = False):
-    """(unique ids, fp32 sums) with duplicates added in arrival order."""
+def dedup_gradients(indices: np.ndarray, grads: np.ndarray, grads_bf16: bool = False, block: int = 0):
+    """(unique ids, fp32 sums) with duplicates added in arrival order (block = 0: one chain per
+    id, the reference's order; block > 0: runs longer than `block` summed block by block)."""
     indices = np.ascontiguousarray(indices)
     dim, gstride = _matrix_params(grads)
     n = indices.shape[0]
     uniq = np.zeros(n, dtype=np.int64)
     sums = np.zeros((max(n, 1), dim), dtype=np.float32)
-    u = lib().wgo_dedup_gradients(_p(indices), _idx_dt(indices), n, _p(grads), wg_dtype(grads, grads_bf16),
-                                  dim, gstride, _p(uniq), _p(sums))
+    u = lib().wgo_dedup_gradients_blocked(_p(indices), _idx_dt(indices), n, _p(grads), wg_dtype(grads, grads_bf16),
+                                          dim, gstride, block, _p(uniq), _p(sums))
     assert u >= 0
     return uniq[:u].copy(), sums[:u].copy()
 

@@ -403,36 +403,64 @@ int wgo_bucket_sort_ids(const void* idx, int idx_dt, int64_t n, const int64_t* o
  * id add its gradient rows one after the other, in arrival order, in fp32.
  *   uniq_ids[n], uniq_grads[n*dim] are filled for the first `return value` entries.
  * grads rows are `grad_stride` elements apart; grad dtype fp32 / fp16 / bf16.
+ * `block` = 0 restates the reference (one chain per id).  `block` > 0 restates what this
+ * repository's kernels do for ids that occur more than `block` times: the run is cut into blocks
+ * of `block` rows in arrival order, each block is summed in order, and the block sums are added
+ * in block order.
  * ------------------------------------------------------------------------------------- */
-int64_t wgo_dedup_gradients(const void* idx, int idx_dt, int64_t n, const void* grads, int grad_dt,
-                            int64_t dim, int64_t grad_stride, int64_t* uniq_ids, float* uniq_grads)
+int64_t wgo_dedup_gradients_blocked(const void* idx, int idx_dt, int64_t n, const void* grads,
+                                    int grad_dt, int64_t dim, int64_t grad_stride, int64_t block,
+                                    int64_t* uniq_ids, float* uniq_grads)
 {
   if (n == 0) return 0;
   kp_t* kp = (kp_t*)malloc(sizeof(kp_t) * (size_t)n);
-  if (!kp) return -1;
+  float* part = (float*)malloc(sizeof(float) * (size_t)(dim > 0 ? dim : 1));
+  if (!kp || !part) return -1;
   for (int64_t i = 0; i < n; i++) {
     kp[i].key = (uint64_t)load_index(idx, idx_dt, i);
     kp[i].pos = i;
   }
   qsort(kp, (size_t)n, sizeof(kp_t), kp_cmp);
-  int64_t u = -1;
-  for (int64_t i = 0; i < n; i++) {
-    int first = (i == 0) || kp[i].key != kp[i - 1].key;
-    if (first) {
-      u++;
-      uniq_ids[u] = (int64_t)kp[i].key;
+  int64_t u = 0;
+  for (int64_t first = 0; first < n;) {
+    int64_t last = first + 1;
+    while (last < n && kp[last].key == kp[first].key) last++;
+    uniq_ids[u] = (int64_t)kp[first].key;
+    float* acc  = uniq_grads + u * dim;
+    int64_t len = last - first;
+    /* block == 0 or a short run: one chain, the reference's order */
+    int64_t step = (block > 0 && len > block) ? block : len;
+    for (int64_t b = first; b < last; b += step) {
+      int64_t e = b + step < last ? b + step : last;
+      for (int64_t i = b; i < e; i++) {
+        for (int64_t c = 0; c < dim; c++) {
+          float g = (float)load_float_elt(grads, grad_dt, kp[i].pos * grad_stride + c);
+          if (i == b)
+            part[c] = g;
+          else
+            part[c] += g;
+        }
+      }
+      for (int64_t c = 0; c < dim; c++) {
+        if (b == first)
+          acc[c] = part[c];
+        else
+          acc[c] += part[c];
+      }
     }
-    float* acc = uniq_grads + u * dim;
-    for (int64_t c = 0; c < dim; c++) {
-      float g = (float)load_float_elt(grads, grad_dt, kp[i].pos * grad_stride + c);
-      if (first)
-        acc[c] = g;
-      else
-        acc[c] += g;
-    }
+    u++;
+    first = last;
   }
   free(kp);
-  return u + 1;
+  free(part);
+  return u;
+}
+
+int64_t wgo_dedup_gradients(const void* idx, int idx_dt, int64_t n, const void* grads, int grad_dt,
+                            int64_t dim, int64_t grad_stride, int64_t* uniq_ids, float* uniq_grads)
+{
+  return wgo_dedup_gradients_blocked(idx, idx_dt, n, grads, grad_dt, dim, grad_stride, 0, uniq_ids,
+                                     uniq_grads);
 }
 
 /* ---------------------------------------------------------------------------------------

@@ -35,7 +35,7 @@ def _read_all(gpu, torch, wg_tensor, rows, dim, dtype):
     return out
 
 
-def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps, n, params, mem_type):
+def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps, n, params, mem_type, block=0):
     import torch
     DT, MT, ML = wgb.WholeGraphDataType, wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation
     tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[table_dtype]
@@ -70,7 +70,7 @@ def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps
         torch.cuda.synchronize()
         wgb.destroy_wholegraph_tensor(wi)
         wgb.destroy_wholegraph_tensor(wg)
-        uniq, sums = orc.dedup_gradients(idx, grads)
+        uniq, sums = orc.dedup_gradients(idx, grads, block=block)
         orc.optimizer_apply(OPTS[opt_name], uniq, sums, w_host, lr=lr,
                             state=state_host if n_states else None, v_offset=padded,
                             beta12t=beta_host if opt_name == "adam" else None,
@@ -116,6 +116,31 @@ def test_gradient_apply_ten_steps_long_chains(gpu, wgb, orc, comm):
     (duplicate chains of ~40 rows), dim 256 as in the sparse-Adam configuration."""
     _run(gpu, wgb, orc, comm, "adam", 256, 256, "f32", np.int64, 10, 10_000, {},
          wgb.WholeGraphMemoryType.MtDistributed)
+
+
+@pytest.mark.parametrize("opt_name", ["adam", "sgd"])
+@pytest.mark.parametrize("dim", [256, 30])
+def test_gradient_apply_runs_longer_than_a_block(gpu, wgb, orc, comm, opt_name, dim):
+    """Ids that occur more than WHOLEGRAPH_B200_DEDUP_BLOCK (256) times in one call: the kernels sum
+    such a run block by block; the oracle restates exactly that order (block=256), so the result
+    is still bit-exact.  12 rows, 20,000 gradient rows per step: every run is ~1,700 long."""
+    _run(gpu, wgb, orc, comm, opt_name, 12, dim, "f32", np.int64, 3, 20_000, {},
+         wgb.WholeGraphMemoryType.MtDistributed, block=256)
+
+
+def test_blocked_sum_stays_close_to_the_single_chain(gpu, orc):
+    """How far the block-by-block order moves a long run's sum from the reference's single chain:
+    bounded by fp32 summation error, far below the gradients' own scale."""
+    rng = np.random.default_rng(0)
+    n, dim = 200_000, 16
+    idx = np.zeros(n, dtype=np.int64)
+    grads = rng.normal(0, 1e-3, size=(n, dim)).astype(np.float32)
+    _, chain = orc.dedup_gradients(idx, grads)
+    _, blocked = orc.dedup_gradients(idx, grads, block=256)
+    exact = grads.astype(np.float64).sum(axis=0)
+    scale = np.abs(grads).sum(axis=0)            # the natural error scale of a sum
+    assert np.all(np.abs(chain[0] - blocked[0]) <= 1e-6 * scale)
+    assert np.all(np.abs(blocked[0] - exact) <= np.abs(chain[0] - exact) + 1e-7 * scale)
 
 
 def test_optimizer_parameter_names(gpu, wgb):
