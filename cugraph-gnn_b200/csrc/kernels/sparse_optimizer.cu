@@ -3,7 +3,8 @@
 //   1. keys_kernel        local row id (or a sentinel) and list position per gradient row
 //   2. cub radix sort     (key, position) pairs, only the bits a local row id can use; stable, so
 //                         equal ids keep their arrival order
-//   3. heads_kernel       compacts the first element of every run of equal keys
+//   3. cub select         first element of every run of equal keys, in order (run r ends where
+//                         run r + 1 starts)
 //   4. apply_kernel       one warp per distinct row: walks its run, adds the gradient rows in
 //                         arrival order (fp32, 16-byte loads, 4 rows in flight), then reads
 //                         weights and state once, updates them and writes them back
@@ -20,6 +21,8 @@
 
 #include <algorithm>
 #include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_select.cuh>
+#include <thrust/iterator/counting_iterator.h>
 
 #include "../common.hpp"
 #include "row_copy.hpp"
@@ -30,6 +33,7 @@ namespace {
 
 constexpr int kThreads    = 256;
 constexpr int kDedupBlock = WHOLEGRAPH_B200_DEDUP_BLOCK;  // rows per block of a long duplicate run
+constexpr int kRowsInFlight = 8;  // gradient rows a lane requests before it starts adding
 
 __global__ void keys_kernel(const void* ids, int is64, int64_t n, int64_t local_start,
                             int64_t local_rows, uint32_t* keys, int32_t* positions)
@@ -43,24 +47,11 @@ __global__ void keys_kernel(const void* ids, int is64, int64_t n, int64_t local_
   positions[i]    = static_cast<int32_t>(i);
 }
 
-// heads[slot] = index (in sorted order) of the first element of a run; *head_count = runs.
-__global__ void heads_kernel(const uint32_t* keys, int64_t n, uint32_t sentinel, int32_t* heads,
-                             int32_t* head_count)
-{
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  bool head       = false;
-  if (i < n) {
-    const uint32_t k = keys[i];
-    head             = k != sentinel && (i == 0 || keys[i - 1] != k);
-  }
-  const unsigned m = __ballot_sync(0xffffffffu, head);
-  if (m == 0) return;
-  const int lane = threadIdx.x & 31;
-  int base       = 0;
-  if (lane == __ffs(m) - 1) base = atomicAdd(head_count, __popc(m));
-  base = __shfl_sync(0xffffffffu, base, __ffs(m) - 1);
-  if (head) heads[base + __popc(m & ((1u << lane) - 1u))] = static_cast<int32_t>(i);
-}
+// True for the first element of every run of equal keys (sorted order).
+struct is_run_head {
+  const uint32_t* keys;
+  __device__ __forceinline__ bool operator()(int i) const { return i == 0 || keys[i] != keys[i - 1]; }
+};
 
 template <typename T>
 __device__ __forceinline__ float load_weight(const T* p)
@@ -115,8 +106,9 @@ __device__ __forceinline__ void store_vec(T* p, const float (&in)[VEC])
 struct apply_params {
   const uint32_t* keys;       // sorted local row ids
   const int32_t* positions;   // list position of each sorted element
-  const int32_t* heads;
-  const int32_t* head_count;
+  const int32_t* heads;       // first sorted element of every run, ascending
+  const int32_t* head_count;  // number of runs (the run of foreign ids, if any, included)
+  uint32_t sentinel;          // key of ids outside this rank's shard
   int64_t n;
   const float* grads;
   int64_t grad_stride;
@@ -173,7 +165,7 @@ __device__ __forceinline__ void update_element(const optimizer_hyper& h, float g
 }
 
 // Sum of the gradient rows of sorted elements [first, last) for columns [c, c + VEC), added one
-// after the other in that order; four rows are requested before the first is added.
+// after the other in that order; kRowsInFlight rows are requested before the first is added.
 template <int VEC>
 __device__ __forceinline__ void sum_rows(const apply_params& p, int64_t first, int64_t last, int c,
                                          float (&acc)[VEC])
@@ -187,11 +179,11 @@ __device__ __forceinline__ void sum_rows(const apply_params& p, int64_t first, i
       acc[0] = __ldg(g0);
     }
   }
-  for (int64_t k = first + 1; k < last; k += 4) {
-    float v[4][VEC];
-    bool on[4];
+  for (int64_t k = first + 1; k < last; k += kRowsInFlight) {
+    float v[kRowsInFlight][VEC];
+    bool on[kRowsInFlight];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < kRowsInFlight; u++) {
       on[u] = k + u < last;
       if (on[u]) {
         const float* g = p.grads + static_cast<int64_t>(p.positions[k + u]) * p.grad_stride + c;
@@ -204,7 +196,7 @@ __device__ __forceinline__ void sum_rows(const apply_params& p, int64_t first, i
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
+    for (int u = 0; u < kRowsInFlight; u++) {
       if (on[u]) {
 #pragma unroll
         for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
@@ -259,21 +251,11 @@ __global__ void __launch_bounds__(kThreads) apply_kernel(const apply_params p)
   W* weights                = static_cast<W*>(p.weights);
 
   for (int64_t run = warp_global; run < runs; run += warp_stride) {
+    // Heads are in sorted order, so a run ends where the next one starts.
     const int64_t first = p.heads[run];
+    const int64_t last  = run + 1 < runs ? p.heads[run + 1] : p.n;
     const uint32_t row  = p.keys[first];
-    // length of the run: lanes probe 32 elements at a time
-    int64_t last = first + 1;
-    while (true) {
-      const int64_t probe = last + lane;
-      const bool same     = probe < p.n && p.keys[probe] == row;
-      const unsigned m    = __ballot_sync(0xffffffffu, same);
-      if (m == 0xffffffffu) {
-        last += 32;
-        continue;
-      }
-      last += __ffs(~m) - 1;
-      break;
-    }
+    if (row == p.sentinel) continue;  // ids this rank does not own sort last
     const int64_t len = last - first;
     if (len > kDedupBlock) {
       const int blocks = static_cast<int>((len + kDedupBlock - 1) / kDedupBlock);
@@ -351,9 +333,22 @@ __global__ void __launch_bounds__(kThreads) apply_long_kernel(const apply_params
       float acc[VEC];
 #pragma unroll
       for (int e = 0; e < VEC; e++) acc[e] = part[c + e];
-      for (int b = 1; b < blocks; b++) {
+      for (int b = 1; b < blocks; b += kRowsInFlight) {
+        float v[kRowsInFlight][VEC];
 #pragma unroll
-        for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], part[static_cast<int64_t>(b) * p.dim + c + e]);
+        for (int u = 0; u < kRowsInFlight; u++) {
+          if (b + u < blocks) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[u][e] = part[static_cast<int64_t>(b + u) * p.dim + c + e];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kRowsInFlight; u++) {
+          if (b + u < blocks) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
+          }
+        }
       }
       update_columns<OPT, W, VEC>(p, w_row, s_row, c, acc, beta1t, beta2t);
     }
@@ -379,7 +374,7 @@ __global__ void round_robin_kernel(const I* ids, I* out, int64_t n, int world, i
 struct workspace_layout {
   size_t keys_in, keys_out, pos_in, pos_out, heads, counters, cub, total;
   size_t long_first, long_len, long_slot, slot_run, slot_block, partial;
-  size_t cub_bytes;
+  size_t cub_bytes, select_bytes;
 };
 
 int key_bits(int64_t local_rows)
@@ -415,6 +410,10 @@ workspace_layout layout_for(int64_t n, int64_t local_rows, int64_t dim)
                                   static_cast<uint32_t*>(nullptr), static_cast<const int32_t*>(nullptr),
                                   static_cast<int32_t*>(nullptr), static_cast<int>(cnt), 0,
                                   key_bits(local_rows));
+  l.select_bytes = 0;
+  cub::DeviceSelect::If(nullptr, l.select_bytes, thrust::counting_iterator<int>(0), static_cast<int32_t*>(nullptr),
+                        static_cast<int32_t*>(nullptr), static_cast<int>(cnt), is_run_head{nullptr});
+  l.cub_bytes = std::max(l.cub_bytes, l.select_bytes);
   l.cub   = off, off += align(l.cub_bytes);
   l.total = off;
   return l;
@@ -507,11 +506,13 @@ void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stre
                                                  static_cast<int>(a.count), 0, key_bits(a.local_rows),
                                                  stream));
   WGB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 3 * sizeof(int32_t), stream));
-  heads_kernel<<<blocks, kThreads, 0, stream>>>(keys_out, a.count, static_cast<uint32_t>(a.local_rows), heads,
-                                                head_count);
+  size_t select_bytes = l.cub_bytes;
+  WGB_CUDA_CHECK(cub::DeviceSelect::If(ws + l.cub, select_bytes, thrust::counting_iterator<int>(0), heads,
+                                       head_count, static_cast<int>(a.count), is_run_head{keys_out}, stream));
 
   apply_params p;
   p.keys = keys_out, p.positions = pos_out, p.heads = heads, p.head_count = head_count, p.n = a.count;
+  p.sentinel = static_cast<uint32_t>(a.local_rows);
   p.grads = a.grads, p.grad_stride = a.grad_stride, p.dim = static_cast<int>(a.dim);
   p.weights = a.weights, p.weight_stride = a.weight_stride;
   p.state = a.state, p.state_stride = a.state_stride, p.v_offset = a.v_offset, p.beta12t = a.beta12t;
