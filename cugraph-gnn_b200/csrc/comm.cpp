@@ -328,6 +328,19 @@ void wholegraph_comm_::alltoallv(const void* send, const int64_t* send_counts,
   WGB_NCCL_CHECK(wgb::nccl_lib().GroupEnd());
 }
 
+void wholegraph_comm_::exchange(const std::vector<transfer>& sends, const std::vector<transfer>& recvs,
+                                cudaStream_t stream)
+{
+  if (world_size == 1) return;
+  ncclComm_t nc = static_cast<ncclComm_t>(nccl);
+  WGB_NCCL_CHECK(wgb::nccl_lib().GroupStart());
+  for (const auto& t : sends)
+    if (t.bytes > 0) WGB_NCCL_CHECK(wgb::nccl_lib().Send(t.ptr, t.bytes, ncclInt8, t.peer, nc, stream));
+  for (const auto& t : recvs)
+    if (t.bytes > 0) WGB_NCCL_CHECK(wgb::nccl_lib().Recv(t.ptr, t.bytes, ncclInt8, t.peer, nc, stream));
+  WGB_NCCL_CHECK(wgb::nccl_lib().GroupEnd());
+}
+
 void wholegraph_comm_::sendrecv(const void* send, size_t send_bytes, int to, void* recv,
                                 size_t recv_bytes, int from, cudaStream_t stream)
 {

@@ -50,6 +50,15 @@ struct wholegraph_comm_ {
   void alltoallv(const void* send, const int64_t* send_counts, const int64_t* send_displs,
                  void* recv, const int64_t* recv_counts, const int64_t* recv_displs,
                  size_t unit_bytes, cudaStream_t stream);
+  // Any number of sends and receives of raw bytes in ONE NCCL group, so that all peers move
+  // data at the same time (empty transfers are skipped; transfers to this rank are not allowed).
+  struct transfer {
+    void* ptr;
+    size_t bytes;
+    int peer;
+  };
+  void exchange(const std::vector<transfer>& sends, const std::vector<transfer>& recvs,
+                cudaStream_t stream);
   // One send and one receive of raw bytes in a single NCCL group (either may be empty).
   void sendrecv(const void* send, size_t send_bytes, int to, void* recv, size_t recv_bytes,
                 int from, cudaStream_t stream);

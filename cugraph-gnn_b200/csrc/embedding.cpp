@@ -227,22 +227,15 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     s0.count         = plan.send_counts[me];
     launch_row_copy(s0, stream);
   }
-  cudaStream_t xs = comm->xchg_stream;
-  for (int s = 1; s < W; s++) {
-    const int to   = (me + s) % W;
-    const int from = (me - s + W) % W;
-    row_copy_args ps = pack;
-    ps.dst           = send + plan.send_displs[to] * row_b;
-    ps.positions     = plan.positions + plan.send_displs[to];
-    ps.count         = plan.send_counts[to];
-    launch_row_copy(ps, stream);
-    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s), stream));
-    WGB_CUDA_CHECK(cudaStreamWaitEvent(xs, comm->event(2 * s), 0));
-    comm->sendrecv(send + plan.send_displs[to] * row_b, plan.send_counts[to] * row_b, to,
-                   recv + plan.recv_displs[from] * row_b, plan.recv_counts[from] * row_b, from, xs);
-  }
-  WGB_CUDA_CHECK(cudaEventRecord(comm->event(1), xs));
-  WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(1), 0));
+  pack.dst = send, pack.positions = plan.positions;
+  pipelined_exchange(
+    comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, send, recv, row_b, stream,
+    [&](const list_segments& seg) {
+      row_copy_args ps = pack;
+      ps.segments = seg, ps.count = seg.total();
+      launch_row_copy(ps, stream);
+    },
+    [](const list_segments&) {});  // the update below needs every row: nothing to do per chunk
   if (plan.total_recv == 0) return;
   a.ids = plan.recv_ids, a.ids_are_64 = true, a.count = plan.total_recv;
   a.grads = reinterpret_cast<const float*>(recv), a.grad_stride = e->dim;

@@ -2,6 +2,7 @@
 
 #include <cuda.h>
 #include <fcntl.h>
+#include <poll.h>
 #include <sys/mman.h>
 #include <sys/socket.h>
 #include <sys/stat.h>
@@ -10,6 +11,7 @@
 
 #include <algorithm>
 #include <cerrno>
+#include <chrono>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -135,7 +137,8 @@ struct fd_exchange {
     if (sock >= 0) close(sock);
   }
 
-  void send_fd(int to, int fd)
+  // Non-blocking: false when the peer's queue is full right now.
+  bool try_send_fd(int to, int fd)
   {
     sockaddr_un a;
     socklen_t len;
@@ -156,11 +159,13 @@ struct fd_exchange {
     c->cmsg_type       = SCM_RIGHTS;
     c->cmsg_len        = CMSG_LEN(sizeof(int));
     memcpy(CMSG_DATA(c), &fd, sizeof(int));
-    if (sendmsg(sock, &msg, 0) < 0) throw system_error(std::string("sendmsg: ") + strerror(errno));
+    if (sendmsg(sock, &msg, MSG_DONTWAIT) >= 0) return true;
+    if (errno == EAGAIN || errno == EWOULDBLOCK || errno == ENOBUFS || errno == EINTR) return false;
+    throw system_error(std::string("sendmsg: ") + strerror(errno));
   }
 
-  // Returns the sender's rank; *fd receives the descriptor.
-  int recv_fd(int* fd)
+  // Non-blocking: false when nothing has arrived yet.
+  bool try_recv_fd(int* from, int* fd)
   {
     int payload = -1;
     iovec iov{&payload, sizeof(payload)};
@@ -170,12 +175,28 @@ struct fd_exchange {
     msg.msg_iovlen     = 1;
     msg.msg_control    = ctrl;
     msg.msg_controllen = sizeof(ctrl);
-    ssize_t n          = recvmsg(sock, &msg, 0);
-    if (n < 0) throw system_error(std::string("recvmsg: ") + strerror(errno));
+    ssize_t n          = recvmsg(sock, &msg, MSG_DONTWAIT);
+    if (n < 0) {
+      if (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) return false;
+      throw system_error(std::string("recvmsg: ") + strerror(errno));
+    }
     cmsghdr* c = CMSG_FIRSTHDR(&msg);
     if (c == nullptr || c->cmsg_type != SCM_RIGHTS) throw system_error("no descriptor in message");
     memcpy(fd, CMSG_DATA(c), sizeof(int));
-    return payload;
+    *from = payload;
+    return true;
+  }
+
+  // Sleep until the socket is readable (or writable, when a send is pending), at most `ms`.
+  void wait_ready(bool want_write, int ms)
+  {
+    pollfd p{sock, static_cast<short>(POLLIN | (want_write ? POLLOUT : 0)), 0};
+    if (want_write) {
+      // A datagram socket is always "writable" even when the peer's queue is full: just nap.
+      usleep(1000);
+      return;
+    }
+    poll(&p, 1, ms);
   }
 };
 
@@ -230,34 +251,41 @@ void alloc_vmm(wholegraph_handle_* h)
   {
     fd_exchange ex(c->tag, h->id, me, W);
     c->barrier();  // every socket is bound
-    // Step s: send to rank+s, expect one message back; keeps socket queues short.
+    // Every rank that holds pages sends its descriptor to every peer; a rank expects one from
+    // every peer that holds pages.  Sends and receives are interleaved without blocking, so no
+    // chain of full socket queues can stall the exchange, whatever subset of ranks sends.
     int expected = 0;
     for (int r = 0; r < W; r++)
       if (r != me && b->map_len[r] > 0) expected++;
-    int got = 0;
-    for (int s = 1; s < W; s++) {
-      int to = (me + s) % W;
-      if (own_fd >= 0) ex.send_fd(to, own_fd);
-      if (got < expected) {
-        int fd   = -1;
-        int from = ex.recv_fd(&fd);
-        WGB_EXPECTS(from >= 0 && from < W && from != me && b->mem[from] == 0, "bad sender %d", from);
-        WGB_CU_CHECK(drv().MemImportFromShareableHandle(
-          &b->mem[from], reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
-          CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
-        close(fd);
-        got++;
+    const int to_send = own_fd >= 0 ? W - 1 : 0;
+    int sent = 0, got = 0;
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(60);
+    while (sent < to_send || got < expected) {
+      bool progressed = false;
+      if (sent < to_send) {
+        const int to = (me + 1 + sent) % W;
+        if (ex.try_send_fd(to, own_fd)) {
+          sent++;
+          progressed = true;
+        }
       }
-    }
-    while (got < expected) {
-      int fd   = -1;
-      int from = ex.recv_fd(&fd);
-      WGB_EXPECTS(from >= 0 && from < W && from != me && b->mem[from] == 0, "bad sender %d", from);
-      WGB_CU_CHECK(drv().MemImportFromShareableHandle(
-        &b->mem[from], reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
-        CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
-      close(fd);
-      got++;
+      if (got < expected) {
+        int fd = -1, from = -1;
+        if (ex.try_recv_fd(&from, &fd)) {
+          WGB_EXPECTS(from >= 0 && from < W && from != me && b->mem[from] == 0, "bad sender %d", from);
+          WGB_CU_CHECK(drv().MemImportFromShareableHandle(
+            &b->mem[from], reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+            CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR));
+          close(fd);
+          got++;
+          progressed = true;
+        }
+      }
+      if (!progressed) {
+        if (std::chrono::steady_clock::now() > deadline)
+          throw system_error("timed out exchanging memory descriptors with the other ranks");
+        ex.wait_ready(sent < to_send, 50);
+      }
     }
     c->barrier();  // nobody closes a socket that still has senders
   }

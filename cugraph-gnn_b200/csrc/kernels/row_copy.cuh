@@ -39,6 +39,7 @@ struct row_copy_params {
   // chunk_offset_bytes is that side's storage offset.
   int64_t chunk_offset_bytes;
   chunked_table chunks;
+  list_segments segments;
 };
 
 // ---- raw vectors of 1..16 bytes ---------------------------------------------------------
@@ -175,6 +176,7 @@ __global__ void __launch_bounds__(kRowCopyThreads, 4)
 {
   __shared__ int64_t s_index[kRowCopyWarps][kRowCopyTile];
   __shared__ int64_t s_position[kRowCopyWarps][kRowCopyTile];
+  __shared__ int64_t s_list[kRowCopyWarps][kRowCopyTile];  // array position of each tile row
 
   const int lane          = threadIdx.x & 31;
   const int warp          = threadIdx.x >> 5;
@@ -194,10 +196,15 @@ __global__ void __launch_bounds__(kRowCopyThreads, 4)
   for (int64_t tile = warp_global; tile < tiles; tile += warp_stride) {
     const int64_t base = tile * kRowCopyTile;
     {
-      const int64_t i = base + lane;
-      int64_t id      = -1;  // positions past the end behave like skipped rows
-      int64_t pos     = 0;
+      int64_t i   = base + lane;
+      int64_t id  = -1;  // positions past the end behave like skipped rows
+      int64_t pos = 0;
       if (i < p.count) {
+        if (p.segments.n > 0) {  // logical -> array position
+          int s = 0;
+          while (s + 1 < p.segments.n && i >= p.segments.prefix[s + 1]) s++;
+          i = p.segments.begin[s] + (i - p.segments.prefix[s]);
+        }
         id = 0;
         if (need_index)
           id = p.indices_are_64 ? __ldg(static_cast<const int64_t*>(p.indices) + i)
@@ -206,6 +213,7 @@ __global__ void __launch_bounds__(kRowCopyThreads, 4)
       }
       s_index[warp][lane]    = id;
       s_position[warp][lane] = pos;
+      s_list[warp][lane]     = i;
     }
     __syncwarp();
 
@@ -221,7 +229,7 @@ __global__ void __launch_bounds__(kRowCopyThreads, 4)
             const int64_t id = s_index[warp][r];
             live[k]          = id >= 0;
             if (live[k]) {
-              const int64_t row = select_row(p.src_select, id, s_position[warp][r], base + r);
+              const int64_t row = select_row(p.src_select, id, s_position[warp][r], s_list[warp][r]);
               const char* src   = src_chunked
                                     ? chunked_row(p.chunks, row, p.src_stride_bytes, p.chunk_offset_bytes)
                                     : p.src + row * p.src_stride_bytes;
@@ -233,7 +241,7 @@ __global__ void __launch_bounds__(kRowCopyThreads, 4)
         for (int k = 0; k < ROWS; k++) {
           if (live[k]) {
             const int r       = r0 + k * rows_per_pass + sub;
-            const int64_t row = select_row(p.dst_select, s_index[warp][r], s_position[warp][r], base + r);
+            const int64_t row = select_row(p.dst_select, s_index[warp][r], s_position[warp][r], s_list[warp][r]);
             char* dst = dst_chunked ? const_cast<char*>(chunked_row(p.chunks, row, p.dst_stride_bytes,
                                                                     p.chunk_offset_bytes))
                                     : p.dst + row * p.dst_stride_bytes;

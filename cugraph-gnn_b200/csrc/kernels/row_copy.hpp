@@ -27,6 +27,25 @@ struct chunked_table {
   int64_t first_row[kMaxChunkedRanks + 1];
 };
 
+// A list made of up to kMaxListSegments disjoint pieces of the index / position / sequential-row
+// arrays: logical position l of the copy maps to array position begin[s] + (l - prefix[s]) for the
+// segment s with prefix[s] <= l < prefix[s + 1].  n = 0 means one piece starting at 0.
+constexpr int kMaxListSegments = 64;
+struct list_segments {
+  int n = 0;
+  int64_t begin[kMaxListSegments];
+  int64_t prefix[kMaxListSegments + 1];
+  void add(int64_t first, int64_t count)
+  {
+    if (count <= 0) return;
+    if (n == 0) prefix[0] = 0;
+    begin[n]      = first;
+    prefix[n + 1] = prefix[n] + count;
+    n++;
+  }
+  int64_t total() const { return n == 0 ? 0 : prefix[n]; }
+};
+
 struct row_copy_args {
   // source rows
   const void* src          = nullptr;  // element 0 of the storage (before src_offset)
@@ -47,6 +66,7 @@ struct row_copy_args {
   bool indices_are_64      = true;
   const int64_t* positions = nullptr;  // for ROW_BY_POSITION
   chunked_table chunks;                // optional, BY_INDEX side only
+  list_segments segments;              // optional; when n > 0, `count` must equal segments.total()
   int sm_hint              = -1;       // -1, or roughly how many SMs to occupy
 };
 

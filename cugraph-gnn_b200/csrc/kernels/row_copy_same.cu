@@ -100,6 +100,8 @@ void launch_row_copy(const row_copy_args& a, cudaStream_t stream)
   p.dst_select         = a.dst_select;
   p.indices_are_64     = a.indices_are_64 ? 1 : 0;
   p.chunks             = a.chunks;
+  p.segments           = a.segments;
+  WGB_EXPECTS(a.segments.n == 0 || a.segments.total() == a.count, "segment list does not add up to count");
   p.chunk_offset_bytes = 0;
   if (chunked)
     p.chunk_offset_bytes = a.src_select == ROW_BY_INDEX ? a.src_offset * es_src : a.dst_offset * es_dst;

@@ -9,6 +9,7 @@
 #include "ops.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <memory>
 #include <vector>
 
@@ -68,6 +69,71 @@ void exchange_plan::build(const void* ids, bool ids_are_64, int64_t n,
   recv_ids = static_cast<int64_t*>(recv_ids_buf.device(total_recv, WHOLEGRAPH_DT_INT64));
   comm->alltoallv(sorted_ids, send_counts.data(), send_displs.data(), recv_ids, recv_counts.data(),
                   recv_displs.data(), sizeof(int64_t), stream);
+}
+
+static int exchange_chunk_count(size_t bytes_out)
+{
+  // WG_EXCHANGE_CHUNKS overrides the number of pipeline chunks (tuning only).
+  static const int forced = [] {
+    const char* e = getenv("WG_EXCHANGE_CHUNKS");
+    return e != nullptr ? std::max(1, atoi(e)) : 0;
+  }();
+  if (forced > 0) return forced;
+  return bytes_out < (size_t(16) << 20) ? 1 : 4;
+}
+
+void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_counts,
+                        const std::vector<int64_t>& out_displs, const std::vector<int64_t>& in_counts,
+                        const std::vector<int64_t>& in_displs, char* out_buf, char* in_buf,
+                        size_t row_bytes, cudaStream_t stream,
+                        const std::function<void(const list_segments&)>& pack,
+                        const std::function<void(const list_segments&)>& unpack)
+{
+  const int W = comm->world_size, me = comm->world_rank;
+  int64_t total_out = 0;
+  for (int p = 0; p < W; p++)
+    if (p != me) total_out += out_counts[p];
+  const int K     = exchange_chunk_count(static_cast<size_t>(total_out) * row_bytes);
+  cudaStream_t xs = comm->xchg_stream;
+  auto cut        = [K](int64_t c, int k, int64_t* b, int64_t* n) {
+    *b = c * k / K;
+    *n = c * (k + 1) / K - *b;
+  };
+  auto segments_of = [&](const std::vector<int64_t>& counts, const std::vector<int64_t>& displs, int k) {
+    list_segments seg;
+    for (int step = 1; step < W; step++) {
+      const int p = (me + step) % W;
+      int64_t b, n;
+      cut(counts[p], k, &b, &n);
+      seg.add(displs[p] + b, n);
+    }
+    return seg;
+  };
+  for (int k = 0; k < K; k++) {
+    const list_segments out_seg = segments_of(out_counts, out_displs, k);
+    if (out_seg.n > 0) pack(out_seg);
+    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * k), stream));
+    WGB_CUDA_CHECK(cudaStreamWaitEvent(xs, comm->event(2 * k), 0));
+    std::vector<wholegraph_comm_::transfer> sends, recvs;
+    for (int step = 1; step < W; step++) {
+      const int to = (me + step) % W, from = (me - step + W) % W;
+      int64_t b, n;
+      cut(out_counts[to], k, &b, &n);
+      sends.push_back({out_buf + (out_displs[to] + b) * row_bytes, static_cast<size_t>(n) * row_bytes, to});
+      cut(in_counts[from], k, &b, &n);
+      recvs.push_back({in_buf + (in_displs[from] + b) * row_bytes, static_cast<size_t>(n) * row_bytes, from});
+    }
+    comm->exchange(sends, recvs, xs);
+    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * k + 1), xs));
+    if (k > 0) {  // overlaps with the exchange just enqueued
+      WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(2 * (k - 1) + 1), 0));
+      const list_segments in_seg = segments_of(in_counts, in_displs, k - 1);
+      if (in_seg.n > 0) unpack(in_seg);
+    }
+  }
+  WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(2 * (K - 1) + 1), 0));
+  const list_segments in_seg = segments_of(in_counts, in_displs, K - 1);
+  if (in_seg.n > 0) unpack(in_seg);
 }
 
 std::vector<int64_t> entry_offsets_of(wholegraph_handle_* h, size_t entry_bytes)
@@ -171,38 +237,27 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
     launch_row_copy(a, stream);
   }
   row_copy_args reorder;  // received rows -> output rows, by position
-  reorder.src_dt = od.dtype, reorder.src_stride = dim, reorder.src_select = ROW_SEQUENTIAL;
+  reorder.src = recv, reorder.src_dt = od.dtype, reorder.src_stride = dim, reorder.src_select = ROW_SEQUENTIAL;
   reorder.dst = out, reorder.dst_dt = od.dtype, reorder.dst_stride = od.stride;
   reorder.dst_offset = od.storage_offset, reorder.dst_select = ROW_BY_POSITION;
-  reorder.dim = dim, reorder.sm_hint = sms;
+  reorder.dim = dim, reorder.sm_hint = sms, reorder.positions = plan.positions;
 
-  cudaStream_t xs = comm->xchg_stream;
-  auto reorder_step = [&](int s) {
-    const int from = (me - s + W) % W;
-    WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(2 * s + 1), 0));
-    row_copy_args r = reorder;
-    r.src           = recv + plan.send_displs[from] * row_b;
-    r.positions     = plan.positions + plan.send_displs[from];
-    r.count         = plan.send_counts[from];
-    launch_row_copy(r, stream);
-  };
-  for (int s = 1; s < W; s++) {
-    const int to   = (me + s) % W;      // whose requests are served now
-    const int from = (me - s + W) % W;  // who serves this rank's requests now
-    row_copy_args a = g;
-    a.dst = serve + plan.recv_displs[to] * row_b, a.dst_stride = dim, a.dst_offset = 0;
-    a.dst_select = ROW_SEQUENTIAL;
-    a.indices    = plan.recv_ids + plan.recv_displs[to];
-    a.count      = plan.recv_counts[to];
-    launch_row_copy(a, stream);
-    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s), stream));
-    WGB_CUDA_CHECK(cudaStreamWaitEvent(xs, comm->event(2 * s), 0));
-    comm->sendrecv(serve + plan.recv_displs[to] * row_b, plan.recv_counts[to] * row_b, to,
-                   recv + plan.send_displs[from] * row_b, plan.send_counts[from] * row_b, from, xs);
-    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s + 1), xs));
-    if (s > 1) reorder_step(s - 1);  // overlaps with the exchange just enqueued
-  }
-  reorder_step(W - 1);
+  row_copy_args serve_rows = g;  // rows other ranks asked for -> serve buffer, in their order
+  serve_rows.dst = serve, serve_rows.dst_stride = dim, serve_rows.dst_offset = 0;
+  serve_rows.dst_select = ROW_SEQUENTIAL, serve_rows.indices = plan.recv_ids;
+
+  pipelined_exchange(
+    comm, plan.recv_counts, plan.recv_displs, plan.send_counts, plan.send_displs, serve, recv, row_b, stream,
+    [&](const list_segments& seg) {
+      row_copy_args a = serve_rows;
+      a.segments = seg, a.count = seg.total();
+      launch_row_copy(a, stream);
+    },
+    [&](const list_segments& seg) {
+      row_copy_args r = reorder;
+      r.segments = seg, r.count = seg.total();
+      launch_row_copy(r, stream);
+    });
 }
 
 // ---- distributed scatter ---------------------------------------------------------------------
@@ -251,36 +306,26 @@ void scatter_distributed(const void* in, const wholegraph_matrix_description_t& 
     a.count      = plan.send_counts[me];
     launch_row_copy(a, stream);
   }
-  cudaStream_t xs = comm->xchg_stream;
-  auto store_step = [&](int s) {
-    const int from = (me - s + W) % W;
-    WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(2 * s + 1), 0));
-    row_copy_args a = put;
-    a.src = recv + plan.recv_displs[from] * row_b, a.src_stride = dim, a.src_offset = 0;
-    a.src_select = ROW_SEQUENTIAL;
-    a.indices    = plan.recv_ids + plan.recv_displs[from];
-    a.count      = plan.recv_counts[from];
-    launch_row_copy(a, stream);
-  };
-  for (int s = 1; s < W; s++) {
-    const int to   = (me + s) % W;
-    const int from = (me - s + W) % W;
-    row_copy_args pack;  // input rows of this peer, in send order
-    pack.src = in, pack.src_dt = id_.dtype, pack.src_stride = id_.stride;
-    pack.src_offset = id_.storage_offset, pack.src_select = ROW_BY_POSITION;
-    pack.dst = send + plan.send_displs[to] * row_b, pack.dst_dt = id_.dtype, pack.dst_stride = dim;
-    pack.dim = dim, pack.sm_hint = sms;
-    pack.positions = plan.positions + plan.send_displs[to];
-    pack.count     = plan.send_counts[to];
-    launch_row_copy(pack, stream);
-    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s), stream));
-    WGB_CUDA_CHECK(cudaStreamWaitEvent(xs, comm->event(2 * s), 0));
-    comm->sendrecv(send + plan.send_displs[to] * row_b, plan.send_counts[to] * row_b, to,
-                   recv + plan.recv_displs[from] * row_b, plan.recv_counts[from] * row_b, from, xs);
-    WGB_CUDA_CHECK(cudaEventRecord(comm->event(2 * s + 1), xs));
-    if (s > 1) store_step(s - 1);
-  }
-  store_step(W - 1);
+  row_copy_args pack;  // input rows, in send order
+  pack.src = in, pack.src_dt = id_.dtype, pack.src_stride = id_.stride;
+  pack.src_offset = id_.storage_offset, pack.src_select = ROW_BY_POSITION;
+  pack.dst = send, pack.dst_dt = id_.dtype, pack.dst_stride = dim;
+  pack.dim = dim, pack.sm_hint = sms, pack.positions = plan.positions;
+  row_copy_args store = put;  // received rows -> local shard
+  store.src = recv, store.src_stride = dim, store.src_offset = 0, store.src_select = ROW_SEQUENTIAL;
+  store.indices = plan.recv_ids;
+  pipelined_exchange(
+    comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, send, recv, row_b, stream,
+    [&](const list_segments& seg) {
+      row_copy_args a = pack;
+      a.segments = seg, a.count = seg.total();
+      launch_row_copy(a, stream);
+    },
+    [&](const list_segments& seg) {
+      row_copy_args a = store;
+      a.segments = seg, a.count = seg.total();
+      launch_row_copy(a, stream);
+    });
   // The reference returns with the local shard updated (scatter_op_impl_nccl.cu:157).
   WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
 }

@@ -4,6 +4,7 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <functional>
 #include <vector>
 
 #include "comm.hpp"
@@ -36,6 +37,23 @@ struct exchange_plan {
  private:
   temp_buffer workspace, sorted_ids_buf, positions_buf, recv_ids_buf, counts_dev, counts_pin;
 };
+
+// Row exchange of a distributed op, cut into chunks so that packing chunk k + 1, moving chunk k
+// over NVLink and unpacking chunk k - 1 overlap.  Rows for peer p occupy
+// [out_displs[p], out_displs[p] + out_counts[p]) of `out_buf` and arrive at
+// [in_displs[p], in_displs[p] + in_counts[p]) of `in_buf`; chunk k of a segment of c rows is rows
+// [c * k / K, c * (k + 1) / K).  `pack(segments)` must enqueue on `stream` whatever fills the
+// outgoing rows named by `segments` (array positions in out_buf's row numbering);
+// `unpack(segments)` consumes the incoming rows named by `segments`.  Every chunk is ONE NCCL
+// group over all peers on the communicator's exchange stream.  On return `stream` is ordered
+// after the last unpack.  The self segment (p == rank) is never touched.
+struct list_segments;
+void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_counts,
+                        const std::vector<int64_t>& out_displs, const std::vector<int64_t>& in_counts,
+                        const std::vector<int64_t>& in_displs, char* out_buf, char* in_buf,
+                        size_t row_bytes, cudaStream_t stream,
+                        const std::function<void(const list_segments&)>& pack,
+                        const std::function<void(const list_segments&)>& unpack);
 
 // First row of every rank's shard (world + 1 entries) for rows of `entry_bytes` bytes.
 std::vector<int64_t> entry_offsets_of(wholegraph_handle_* h, size_t entry_bytes);

@@ -1,0 +1,131 @@
+"""Cross-check against the reference's OWN device code (oracle/_ref/libwg_ref_kernels.so, built
+from the reference's sources by `make -C oracle ref` where the reference checkout exists).
+
+Gather and scatter: the reference kernel, the CPU oracle and this repository's kernel must agree
+bit for bit.  Optimizers: the reference kernels are compiled with nvcc's default fused
+multiply-add contraction, the oracle and this repository's kernels round every operation
+separately (like the reference's CPU test optimizer), so they are compared within the
+1e-6 relative bound of the task, with an absolute floor of 1e-7 for values near zero."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+REF = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libwg_ref_kernels.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF):
+        pytest.skip("reference kernels were not built (no reference checkout at build time)")
+    lib = C.CDLL(REF, mode=C.RTLD_LOCAL)
+    vp, i64, ci, f = C.c_void_p, C.c_int64, C.c_int, C.c_float
+    lib.wgref_gather.argtypes = [vp, ci, i64, i64, i64, i64, vp, ci, i64, vp, ci, i64, i64, vp]
+    lib.wgref_scatter.argtypes = [vp, ci, i64, i64, i64, vp, ci, i64, vp, ci, i64, i64, i64, vp]
+    lib.wgref_optimizer_step.argtypes = [ci, vp, vp, i64, vp, ci, vp, vp, i64, ci, ci, ci, f, f, f, f, f, f, ci, vp]
+    return lib
+
+
+TORCH = {1: "float32", 2: "float16", 4: "bfloat16"}
+
+
+def _bits(torch, t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy()
+
+
+@pytest.mark.parametrize("tab_dt,out_dt", [(1, 1), (1, 2), (1, 4), (2, 2), (2, 1), (2, 4), (4, 4), (4, 1), (4, 2)])
+@pytest.mark.parametrize("dim,stride,offset", [(1, 1, 0), (11, 11, 0), (32, 32, 0), (127, 127, 0), (128, 128, 0),
+                                               (129, 129, 0), (513, 513, 0), (32, 33, 1), (64, 72, 8)])
+@pytest.mark.parametrize("idx64", [0, 1])
+def test_gather_three_way(gpu, wgb, orc, ref, tab_dt, out_dt, dim, stride, offset, idx64):
+    import torch
+    rows, n = 20_000, 5_003
+    rng = np.random.default_rng(dim * 7 + tab_dt + out_dt)
+    storage = torch.from_numpy(rng.uniform(-1, 1, size=offset + rows * stride).astype(np.float32)).cuda().to(getattr(torch, TORCH[tab_dt]))
+    idx_np = rng.integers(0, rows, size=n)
+    idx_np[::41] = -1
+    idx = torch.from_numpy(idx_np.astype(np.int64 if idx64 else np.int32)).cuda()
+    fill = torch.full((n, dim), 3.0, dtype=getattr(torch, TORCH[out_dt]), device="cuda")
+    out_ref, out_mine = fill.clone(), fill.clone()
+    s = torch.cuda.current_stream().cuda_stream
+    rc = ref.wgref_gather(storage.data_ptr(), tab_dt, rows, dim, stride, offset, idx.data_ptr(), idx64, n,
+                          out_ref.data_ptr(), out_dt, dim, 0, s)
+    assert rc == 0
+    desc = wgb.make_description([rows, dim], wgb.WholeGraphDataType(tab_dt), strides=[stride, 1], storage_offset=offset)
+    wt = wgb.make_tensor_from_pointer(storage.data_ptr(), desc)
+    gpu.gather(wt, idx, out_mine)
+    torch.cuda.synchronize()
+    wgb.destroy_wholegraph_tensor(wt)
+    host = _bits(torch, storage)
+    view = host[offset:offset + rows * stride].reshape(rows, stride)[:, :dim]
+    want = np.ascontiguousarray(_bits(torch, fill))
+    orc.gather(view, idx.cpu().numpy(), out_dt=out_dt, out=want, table_bf16=(tab_dt == 4))
+    assert np.array_equal(_bits(torch, out_ref).view(want.dtype), want), "reference kernel differs from the oracle"
+    assert np.array_equal(_bits(torch, out_mine).view(want.dtype), want), "this repository's kernel differs from the oracle"
+
+
+@pytest.mark.parametrize("in_dt,tab_dt", [(1, 1), (2, 1), (1, 2), (4, 1), (1, 4), (2, 2)])
+@pytest.mark.parametrize("dim,stride", [(11, 12), (128, 128), (129, 131), (513, 513)])
+def test_scatter_three_way(gpu, wgb, orc, ref, in_dt, tab_dt, dim, stride):
+    import torch
+    rows, n = 9_000, 2_500
+    rng = np.random.default_rng(dim + in_dt * 10 + tab_dt)
+    base = torch.from_numpy(rng.uniform(-1, 1, size=rows * stride).astype(np.float32)).cuda().to(getattr(torch, TORCH[tab_dt]))
+    t_ref, t_mine = base.clone(), base.clone()
+    idx_np = rng.permutation(rows)[:n].astype(np.int64)
+    idx_np[3] = -1
+    idx = torch.from_numpy(idx_np).cuda()
+    inp = torch.from_numpy(rng.uniform(-1, 1, size=(n, dim)).astype(np.float32)).cuda().to(getattr(torch, TORCH[in_dt]))
+    s = torch.cuda.current_stream().cuda_stream
+    assert ref.wgref_scatter(inp.data_ptr(), in_dt, dim, dim, 0, idx.data_ptr(), 1, n, t_ref.data_ptr(), tab_dt, rows,
+                             stride, 0, s) == 0
+    desc = wgb.make_description([rows, dim], wgb.WholeGraphDataType(tab_dt), strides=[stride, 1])
+    wt = wgb.make_tensor_from_pointer(t_mine.data_ptr(), desc)
+    gpu.scatter(inp, idx, wt)
+    torch.cuda.synchronize()
+    wgb.destroy_wholegraph_tensor(wt)
+    want = _bits(torch, base).copy()
+    orc.scatter(np.ascontiguousarray(_bits(torch, inp)), idx_np, want.reshape(rows, stride)[:, :dim],
+                rows_bf16=(in_dt == 4), table_bf16=(tab_dt == 4))
+    assert np.array_equal(_bits(torch, t_ref).view(want.dtype), want), "reference kernel differs from the oracle"
+    assert np.array_equal(_bits(torch, t_mine).view(want.dtype), want), "this repository's kernel differs from the oracle"
+
+
+def _close(a, b, rel=1e-6, floor=1e-7):
+    a, b = a.astype(np.float64), b.astype(np.float64)
+    return np.all(np.abs(a - b) <= rel * np.maximum(np.abs(a), np.abs(b)) + floor)
+
+
+@pytest.mark.parametrize("opt,code", [("sgd", 1), ("adam", 2), ("rmsprop", 3), ("adagrad", 4)])
+@pytest.mark.parametrize("dim", [3, 32, 129, 256])
+def test_optimizer_kernels_against_reference(gpu, wgb, orc, ref, opt, code, dim):
+    import torch
+    rows, n, steps = 3_000, 1_500, 5
+    rng = np.random.default_rng(dim + code)
+    padded = -(-dim // 4) * 4
+    w0 = rng.normal(0, 0.01, size=(rows, padded)).astype(np.float32)
+    w_ref = torch.from_numpy(w0).cuda()
+    n_states = 2 if opt == "adam" else 1          # state rows are n_states * padded floats wide
+    st_ref = torch.zeros((rows, n_states * padded), dtype=torch.float32, device="cuda")
+    b_ref = torch.ones((rows, 2), dtype=torch.float32, device="cuda")
+    w_orc, st_orc, b_orc = w0.copy(), np.zeros((rows, n_states * padded), np.float32), np.ones((rows, 2), np.float32)
+    s = torch.cuda.current_stream().cuda_stream
+    for step in range(steps):
+        ids = np.sort(rng.permutation(rows)[:n]).astype(np.int64)          # already unique
+        grads = rng.normal(0, 1e-3, size=(n, dim)).astype(np.float32)
+        d_ids, d_g = torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda()
+        rc = ref.wgref_optimizer_step(code, d_ids.data_ptr(), d_g.data_ptr(), n, w_ref.data_ptr(), 1, st_ref.data_ptr(),
+                                      b_ref.data_ptr(), 0, dim, dim, padded, 1e-3, 0.01, 1e-8, 0.9, 0.999, 0.99, 0, s)
+        assert rc == 0
+        torch.cuda.synchronize()
+        orc.optimizer_apply(code, ids, grads, w_orc, lr=1e-3, state=st_orc, v_offset=padded, beta12t=b_orc,
+                            weight_decay=0.01)
+    got_w, got_s = w_ref.cpu().numpy(), st_ref.cpu().numpy()
+    assert _close(got_w[:, :dim], w_orc[:, :dim]), f"weights: max abs diff {np.abs(got_w[:, :dim] - w_orc[:, :dim]).max()}"
+    assert _close(got_s[:, :dim], st_orc[:, :dim])
+    if opt == "adam":
+        assert _close(got_s[:, padded:padded + dim], st_orc[:, padded:padded + dim])
+    if opt == "adam":
+        assert np.array_equal(b_ref.cpu().numpy(), b_orc)
