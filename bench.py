@@ -111,11 +111,14 @@ class ClockSampler:
         return out
 
 
-def zipf_ids(torch, n, rows, alpha, perm, gen):
-    """Bounded power-law ranks by inverse CDF, mapped through a permutation of the row ids."""
+def zipf_ids(torch, n, rows, alpha, perm, gen, shift=0.0):
+    """Bounded power-law ranks P(k) ~ (k + shift)^-alpha by inverse CDF, mapped through a permutation
+    of the row ids.  shift = 0 is a plain bounded Zipf; a positive shift (Zipf-Mandelbrot) flattens
+    the head and is how a stated duplicate rate is met."""
     u = torch.rand(n, generator=gen, device="cuda", dtype=torch.float64)
     e = 1.0 - alpha
-    rank = torch.floor(((float(rows) ** e - 1.0) * u + 1.0) ** (1.0 / e)).to(torch.int64)
+    lo, hi = (1.0 + shift) ** e, (float(rows) + shift) ** e
+    rank = torch.floor(((hi - lo) * u + lo) ** (1.0 / e) - shift).to(torch.int64)
     rank = rank.clamp_(1, rows) - 1
     return perm[rank] if perm is not None else rank
 
@@ -314,7 +317,7 @@ def main():
         run_sparse_adam(args, torch, dist, wgb, tu, comm, world, rank, local_rank)
         return
     MT = wgb.WholeGraphMemoryType
-    mem_type, zipf_alpha = MT.MtContinuous, None
+    mem_type, zipf_alpha, zipf_shift = MT.MtContinuous, None, 0.0
     if workload == "c2":
         n_ids = args.ids or IDS_PER_RANK
         rows = args.rows or 10_000_000
@@ -330,10 +333,12 @@ def main():
     else:
         n_ids = args.ids or 4_194_304
         rows = args.rows or 240_000_000
-        zipf_alpha, mem_type = 1.2, MT.MtDistributed
+        # Zipf-Mandelbrot shift calibrated so that a 4,194,304-id request over 240 M rows holds
+        # about 30 % duplicates, the rate the configuration states.
+        zipf_alpha, zipf_shift, mem_type = 1.2, 1.4e5, MT.MtDistributed
         tab_dtype, out_dtype, tab_wg = torch.bfloat16, torch.bfloat16, wgb.WholeGraphDataType.DtBF16
         name = (f"C4: {rows} x {ROW_DIM} bf16 table row-sharded DISTRIBUTED (NCCL exchange) over {world} GPUs, "
-                f"{n_ids} int64 Zipf(1.2) ids per rank over a seeded permutation, bf16 output")
+                f"{n_ids} int64 Zipf(1.2, shift 1.4e5: ~30% duplicates) ids per rank over a seeded permutation, bf16 output")
     es_tab = torch.empty((), dtype=tab_dtype).element_size()
     es_out = torch.empty((), dtype=out_dtype).element_size()
 
@@ -360,7 +365,7 @@ def main():
         perm = torch.randperm(rows, generator=torch.Generator(device="cuda").manual_seed(7), device="cuda")
         for b in range(INDEX_BATCHES):
             g = torch.Generator(device="cuda").manual_seed(100 + rank + 1000 * b)
-            batches.append(zipf_ids(torch, n_ids, rows, zipf_alpha, perm, g))
+            batches.append(zipf_ids(torch, n_ids, rows, zipf_alpha, perm, g, zipf_shift))
         del perm
         torch.cuda.empty_cache()
     out = torch.empty((n_ids, ROW_DIM), dtype=out_dtype, device="cuda")

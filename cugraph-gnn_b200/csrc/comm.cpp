@@ -93,7 +93,11 @@ void setup_staging(wholegraph_comm_* c)
 {
   WGB_CUDA_CHECK(cudaGetDevice(&c->dev_id));
   WGB_CUDA_CHECK(cudaStreamCreateWithFlags(&c->side_stream, cudaStreamNonBlocking));
-  WGB_CUDA_CHECK(cudaStreamCreateWithFlags(&c->xchg_stream, cudaStreamNonBlocking));
+  // The exchange stream gets the highest priority: its NCCL kernels need only a few CTAs and
+  // must not queue behind the thousands of short CTAs of the copy kernels they overlap with.
+  int prio_low = 0, prio_high = 0;
+  WGB_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&prio_low, &prio_high));
+  WGB_CUDA_CHECK(cudaStreamCreateWithPriority(&c->xchg_stream, cudaStreamNonBlocking, prio_high));
   c->stage_bytes = (size_t(1) << 20) * static_cast<size_t>(c->world_size) * 2;
   if (c->world_size > 1) {
     WGB_CUDA_CHECK(cudaMalloc(&c->dev_stage, c->stage_bytes));

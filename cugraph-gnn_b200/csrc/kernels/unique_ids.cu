@@ -1,0 +1,180 @@
+// De-duplication of a gather's request list before it goes on the wire.
+//
+// A skewed request list (a GNN mini-batch hits hub nodes again and again) sends the same id to
+// the same owner many times; the owner of a hot row then serves - and its NVLink egress
+// carries - several times the average.  Sorting the ids once gives both the grouping by owner
+// (shards are contiguous row ranges) and the runs of equal ids, so only distinct ids travel and
+// every row comes back once; the requester expands the rows with one more local gather.
+//
+//   1. keys_kernel      valid id -> 32-bit key, everything else -> sentinel; value = list position
+//   2. cub radix sort   (key, position) pairs over the bits a row id can use
+//   3. cub scan         running count of run heads -> slot of every sorted element
+//   4. emit_kernel      unique_ids[slot] = key at run heads; inverse[position] = slot
+//   5. bounds_kernel    per-owner group boundaries by binary search in the distinct ids
+#include "unique_ids.hpp"
+
+#include <algorithm>
+#include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
+#include <thrust/iterator/counting_iterator.h>
+#include <thrust/iterator/transform_iterator.h>
+
+#include "../common.hpp"
+#include "partition.hpp"
+#include "row_copy.hpp"
+
+namespace wgb {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__global__ void keys_kernel(const void* ids, int is64, int64_t n, int64_t total_rows, uint32_t* keys,
+                            int32_t* positions)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t id = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
+                          : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
+  keys[i]      = (id >= 0 && id < total_rows) ? static_cast<uint32_t>(id) : static_cast<uint32_t>(total_rows);
+  positions[i] = static_cast<int32_t>(i);
+}
+
+struct head_flag {
+  const uint32_t* keys;
+  uint32_t sentinel;
+  __device__ __forceinline__ int operator()(int j) const
+  {
+    const uint32_t k = keys[j];
+    return (k != sentinel && (j == 0 || keys[j - 1] != k)) ? 1 : 0;
+  }
+};
+
+__global__ void emit_kernel(const uint32_t* keys, const int32_t* positions, const int32_t* run_index,
+                            int64_t n, uint32_t sentinel, int64_t* unique_ids, int64_t* inverse)
+{
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const uint32_t k = keys[j];
+  if (k == sentinel) {
+    inverse[positions[j]] = -1;
+    return;
+  }
+  const int slot        = run_index[j] - 1;
+  inverse[positions[j]] = slot;
+  if (j == 0 || keys[j - 1] != k) unique_ids[slot] = k;
+}
+
+struct bounds_args {
+  int world;
+  int64_t first_row[kMaxPartitionRanks + 1];
+};
+
+// starts[r] = first slot whose id is >= first_row[r]; counts[r] = starts[r + 1] - starts[r].
+__global__ void bounds_kernel(const int64_t* unique_ids, const int32_t* run_index, int64_t n, bounds_args a,
+                              int64_t* counts, int64_t* starts)
+{
+  __shared__ int64_t s_start[kMaxPartitionRanks + 1];
+  const int64_t distinct = run_index[n - 1];
+  const int r            = threadIdx.x;
+  if (r <= a.world) {
+    int64_t lo = 0, hi = distinct;
+    const int64_t target = a.first_row[r];
+    while (lo < hi) {
+      const int64_t mid = (lo + hi) >> 1;
+      if (unique_ids[mid] < target)
+        lo = mid + 1;
+      else
+        hi = mid;
+    }
+    s_start[r] = lo;
+  }
+  __syncthreads();
+  if (r < a.world) {
+    starts[r] = s_start[r];
+    counts[r] = s_start[r + 1] - s_start[r];
+  }
+}
+
+int key_bits(int64_t total_rows)
+{
+  int bits = 1;
+  while (bits < 32 && (int64_t(1) << bits) <= total_rows) bits++;
+  return bits;
+}
+
+struct layout {
+  size_t keys_in, keys_out, pos_in, pos_out, run_index, cub, total, cub_bytes;
+};
+
+layout layout_for(int64_t n, int64_t total_rows)
+{
+  layout l{};
+  auto align       = [](size_t x) { return (x + 255) / 256 * 256; };
+  const size_t cnt = static_cast<size_t>(std::max<int64_t>(n, 1));
+  size_t off       = 0;
+  l.keys_in = off, off += align(cnt * 4);
+  l.keys_out = off, off += align(cnt * 4);
+  l.pos_in = off, off += align(cnt * 4);
+  l.pos_out = off, off += align(cnt * 4);
+  l.run_index = off, off += align(cnt * 4);
+  size_t sort_bytes = 0, scan_bytes = 0;
+  cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, static_cast<const uint32_t*>(nullptr),
+                                  static_cast<uint32_t*>(nullptr), static_cast<const int32_t*>(nullptr),
+                                  static_cast<int32_t*>(nullptr), static_cast<int>(cnt), 0, key_bits(total_rows));
+  auto flags = thrust::make_transform_iterator(thrust::counting_iterator<int>(0), head_flag{nullptr, 0});
+  cub::DeviceScan::InclusiveSum(nullptr, scan_bytes, flags, static_cast<int32_t*>(nullptr), static_cast<int>(cnt));
+  l.cub_bytes = std::max(sort_bytes, scan_bytes);
+  l.cub = off, off += align(l.cub_bytes);
+  l.total = off;
+  return l;
+}
+
+}  // namespace
+
+bool unique_supported(int64_t n, int64_t total_rows)
+{
+  return n < (int64_t(1) << 31) && total_rows < (int64_t(1) << 32) - 1;
+}
+
+size_t unique_workspace_bytes(int64_t n, int64_t total_rows) { return layout_for(n, total_rows).total; }
+
+void unique_by_owner(const void* ids, bool ids_are_64, int64_t n, const int64_t* first_row, int world,
+                     void* workspace, int64_t* unique_ids, int64_t* inverse, int64_t* counts,
+                     int64_t* starts, cudaStream_t stream)
+{
+  WGB_EXPECTS(world >= 1 && world <= kMaxPartitionRanks, "world size %d exceeds %d", world, kMaxPartitionRanks);
+  const int64_t total_rows = first_row[world];
+  WGB_EXPECTS(unique_supported(n, total_rows), "request list or table too large for 32-bit sort keys");
+  if (n == 0) {
+    WGB_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * world, stream));
+    WGB_CUDA_CHECK(cudaMemsetAsync(starts, 0, sizeof(int64_t) * world, stream));
+    return;
+  }
+  const layout l        = layout_for(n, total_rows);
+  char* ws              = static_cast<char*>(workspace);
+  auto* keys_in         = reinterpret_cast<uint32_t*>(ws + l.keys_in);
+  auto* keys_out        = reinterpret_cast<uint32_t*>(ws + l.keys_out);
+  auto* pos_in          = reinterpret_cast<int32_t*>(ws + l.pos_in);
+  auto* pos_out         = reinterpret_cast<int32_t*>(ws + l.pos_out);
+  auto* run_index       = reinterpret_cast<int32_t*>(ws + l.run_index);
+  const unsigned blocks = static_cast<unsigned>((n + kThreads - 1) / kThreads);
+  const uint32_t sentinel = static_cast<uint32_t>(total_rows);
+
+  keys_kernel<<<blocks, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, total_rows, keys_in, pos_in);
+  size_t bytes = l.cub_bytes;
+  WGB_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(ws + l.cub, bytes, keys_in, keys_out, pos_in, pos_out,
+                                                 static_cast<int>(n), 0, key_bits(total_rows), stream));
+  auto flags = thrust::make_transform_iterator(thrust::counting_iterator<int>(0), head_flag{keys_out, sentinel});
+  bytes      = l.cub_bytes;
+  WGB_CUDA_CHECK(cub::DeviceScan::InclusiveSum(ws + l.cub, bytes, flags, run_index, static_cast<int>(n), stream));
+  emit_kernel<<<blocks, kThreads, 0, stream>>>(keys_out, pos_out, run_index, n, sentinel, unique_ids, inverse);
+  bounds_args a;
+  a.world = world;
+  for (int r = 0; r <= world; r++) a.first_row[r] = first_row[r];
+  bounds_kernel<<<1, kMaxPartitionRanks + 1 + 31, 0, stream>>>(unique_ids, run_index, n, a, counts, starts);
+  count_kernel_launch(5);
+  WGB_LAUNCH_CHECK(stream);
+}
+
+}  // namespace wgb

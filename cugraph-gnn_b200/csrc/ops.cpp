@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <memory>
+#include <string>
 #include <vector>
 
 #include <wholegraph/wholegraph_tensor_op.h>
@@ -20,6 +21,7 @@
 #include "handle.hpp"
 #include "kernels/partition.hpp"
 #include "kernels/row_copy.hpp"
+#include "kernels/unique_ids.hpp"
 #include "tensor.hpp"
 
 namespace wgb {
@@ -34,7 +36,7 @@ exchange_plan::exchange_plan(wholegraph_env_func_t* env)
 
 void exchange_plan::build(const void* ids, bool ids_are_64, int64_t n,
                           const std::vector<int64_t>& first_row, wholegraph_comm_* comm,
-                          cudaStream_t stream)
+                          cudaStream_t stream, bool dedup)
 {
   world = comm->world_size;
   me    = comm->world_rank;
@@ -44,14 +46,22 @@ void exchange_plan::build(const void* ids, bool ids_are_64, int64_t n,
   recv_counts.assign(world, 0);
   recv_displs.assign(world, 0);
 
-  void* ws   = workspace.device_bytes(partition_workspace_bytes(n, world));
   sorted_ids = static_cast<int64_t*>(sorted_ids_buf.device(n, WHOLEGRAPH_DT_INT64));
   positions  = static_cast<int64_t*>(positions_buf.device(n, WHOLEGRAPH_DT_INT64));
   // Device layout: [send counts | send starts | recv counts], world entries each.
   int64_t* cdev = static_cast<int64_t*>(counts_dev.device(3 * world, WHOLEGRAPH_DT_INT64));
   int64_t* cpin = static_cast<int64_t*>(counts_pin.pinned(3 * world, WHOLEGRAPH_DT_INT64));
-  partition_by_owner(ids, ids_are_64, n, first_row.data(), world, ws, sorted_ids, positions, cdev,
-                     cdev + world, stream);
+  if (dedup) {
+    void* ws = workspace.device_bytes(unique_workspace_bytes(n, first_row[world]));
+    inverse  = positions;  // same storage, other meaning
+    unique_by_owner(ids, ids_are_64, n, first_row.data(), world, ws, sorted_ids, inverse, cdev, cdev + world,
+                    stream);
+    positions = nullptr;
+  } else {
+    void* ws = workspace.device_bytes(partition_workspace_bytes(n, world));
+    partition_by_owner(ids, ids_are_64, n, first_row.data(), world, ws, sorted_ids, positions, cdev,
+                       cdev + world, stream);
+  }
   comm->alltoall(cdev, cdev + 2 * world, sizeof(int64_t), stream);
   WGB_CUDA_CHECK(cudaMemcpyAsync(cpin, cdev, sizeof(int64_t) * 3 * world, cudaMemcpyDeviceToHost,
                                  stream));
@@ -70,6 +80,45 @@ void exchange_plan::build(const void* ids, bool ids_are_64, int64_t n,
   comm->alltoallv(sorted_ids, send_counts.data(), send_displs.data(), recv_ids, recv_counts.data(),
                   recv_displs.data(), sizeof(int64_t), stream);
 }
+
+// WG_TIMING=1: distributed gathers record CUDA events at their phase boundaries and print the
+// phase durations (this synchronises the stream; diagnosis only).
+struct phase_timer {
+  bool on;
+  cudaStream_t stream;
+  std::vector<std::pair<const char*, cudaEvent_t>> marks;
+  explicit phase_timer(cudaStream_t s) : stream(s)
+  {
+    static const bool enabled = [] {
+      const char* e = getenv("WG_TIMING");
+      return e != nullptr && e[0] == '1';
+    }();
+    on = enabled;
+  }
+  void mark(const char* name)
+  {
+    if (!on) return;
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    cudaEventRecord(e, stream);
+    marks.push_back({name, e});
+  }
+  ~phase_timer()
+  {
+    if (!on || marks.empty()) return;
+    cudaStreamSynchronize(stream);
+    std::string line;
+    for (size_t i = 1; i < marks.size(); i++) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
+      line += format_string(" %s=%.3f", marks[i].first, ms);
+    }
+    float total = 0.f;
+    cudaEventElapsedTime(&total, marks.front().second, marks.back().second);
+    fprintf(stderr, "[wholegraph timing]%s total=%.3f ms\n", line.c_str(), total);
+    for (auto& m : marks) cudaEventDestroy(m.second);
+  }
+};
 
 static int exchange_chunk_count(size_t bytes_out)
 {
@@ -219,8 +268,53 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
     return;
   }
 
+  phase_timer timer(stream);
+  timer.mark("start");
   exchange_plan plan(env);
-  plan.build(ids, ids_are_64, n, first_row, comm, stream);
+  // WG_GATHER_DEDUP=0 routes every request, duplicates included, as the reference does.
+  static const bool dedup_wanted = [] {
+    const char* e = getenv("WG_GATHER_DEDUP");
+    return e == nullptr || e[0] != '0';
+  }();
+  const bool dedup = dedup_wanted && unique_supported(n, first_row[W]);
+  plan.build(ids, ids_are_64, n, first_row, comm, stream, dedup);
+  timer.mark(dedup ? "unique+counts+ids" : "partition+counts+ids");
+
+  if (dedup) {
+    // Distinct ids only: owners serve each row once into `rows` (own rows are gathered into
+    // their slots locally), then one local gather expands them into the output.
+    temp_buffer serve_buf(env), rows_buf(env);
+    char* serve = static_cast<char*>(serve_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
+    char* rows  = static_cast<char*>(rows_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
+    row_copy_args from_shard = g;  // local shard -> dense rows, by index, cast at the owner
+    from_shard.dst_stride = dim, from_shard.dst_offset = 0, from_shard.dst_select = ROW_SEQUENTIAL;
+    if (plan.send_counts[me] > 0) {
+      row_copy_args a = from_shard;
+      a.dst = rows, a.indices = plan.sorted_ids;
+      a.segments.add(plan.send_displs[me], plan.send_counts[me]);
+      a.count = a.segments.total();
+      launch_row_copy(a, stream);
+    }
+    timer.mark("own_rows");
+    pipelined_exchange(
+      comm, plan.recv_counts, plan.recv_displs, plan.send_counts, plan.send_displs, serve, rows, row_b, stream,
+      [&](const list_segments& seg) {
+        row_copy_args a = from_shard;
+        a.dst = serve, a.indices = plan.recv_ids;
+        a.segments = seg, a.count = seg.total();
+        launch_row_copy(a, stream);
+      },
+      [](const list_segments&) {});
+    timer.mark("exchange");
+    row_copy_args expand;  // rows[inverse[i]] -> output row i; ids nobody owns leave their row untouched
+    expand.src = rows, expand.src_dt = od.dtype, expand.src_stride = dim, expand.src_select = ROW_BY_INDEX;
+    expand.dst = out, expand.dst_dt = od.dtype, expand.dst_stride = od.stride, expand.dst_offset = od.storage_offset;
+    expand.dst_select = ROW_SEQUENTIAL, expand.dim = dim, expand.sm_hint = sms;
+    expand.indices = plan.inverse, expand.indices_are_64 = true, expand.count = n;
+    launch_row_copy(expand, stream);
+    timer.mark("expand");
+    return;
+  }
 
   temp_buffer serve_buf(env), recv_buf(env);
   char* serve = static_cast<char*>(serve_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
@@ -236,6 +330,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
     a.count      = plan.send_counts[me];
     launch_row_copy(a, stream);
   }
+  timer.mark("own_rows");
   row_copy_args reorder;  // received rows -> output rows, by position
   reorder.src = recv, reorder.src_dt = od.dtype, reorder.src_stride = dim, reorder.src_select = ROW_SEQUENTIAL;
   reorder.dst = out, reorder.dst_dt = od.dtype, reorder.dst_stride = od.stride;
@@ -258,6 +353,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
       r.segments = seg, r.count = seg.total();
       launch_row_copy(r, stream);
     });
+  timer.mark("exchange+reorder");
 }
 
 // ---- distributed scatter ---------------------------------------------------------------------

@@ -21,8 +21,11 @@ struct exchange_plan {
 
   // Partition `ids` by owner, exchange the per-rank counts (one host synchronisation of
   // `stream`) and then the ids themselves (asynchronous on `stream`).
+  // With `dedup`, only the distinct valid ids are routed (ascending inside each owner's group):
+  // sorted_ids then holds them, `inverse[i]` is the slot of list position i in sorted_ids (-1 for
+  // ids nobody owns) and `positions` is not filled.
   void build(const void* ids, bool ids_are_64, int64_t n, const std::vector<int64_t>& first_row,
-             wholegraph_comm_* comm, cudaStream_t stream);
+             wholegraph_comm_* comm, cudaStream_t stream, bool dedup = false);
 
   int world = 1, me = 0;
   int64_t count = 0;  // length of the request list
@@ -33,6 +36,7 @@ struct exchange_plan {
   int64_t* sorted_ids = nullptr;  // device, global row ids grouped by owner
   int64_t* positions  = nullptr;  // device, list position of each sorted id
   int64_t* recv_ids   = nullptr;  // device, global row ids this rank must serve
+  int64_t* inverse    = nullptr;  // device, dedup only: slot in sorted_ids of every list position
 
  private:
   temp_buffer workspace, sorted_ids_buf, positions_buf, recv_ids_buf, counts_dev, counts_pin;

@@ -19,13 +19,16 @@ def _device_count():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.parametrize("scenario", ["continuous", "distributed", "chunked", "optimizer"])
+@pytest.mark.parametrize("scenario", ["continuous", "distributed", "distributed-keepdups", "chunked", "optimizer"])
 def test_multi_gpu_gather_scatter(scenario):
     world = min(_device_count(), int(os.environ.get("WG_TEST_WORLD", "8")))
     if world < 2:
         pytest.skip("needs at least two GPUs")
     with tempfile.TemporaryDirectory() as rdv:
         env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        if scenario.endswith("-keepdups"):       # the path that routes duplicates, as the reference does
+            env["WG_GATHER_DEDUP"] = "0"
+            scenario = scenario.split("-")[0]
         logs = [open(os.path.join(rdv, f"rank{r}.log"), "w+") for r in range(world)]
         procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "mg_worker.py"), str(r), str(world), rdv, scenario],
                                   env=env, stdout=logs[r], stderr=subprocess.STDOUT, text=True)
