@@ -203,6 +203,8 @@ def _declare(lib: C.CDLL) -> None:
         "wholegraph_embedding_gather_gradient_apply": (C.c_int, [vp, vp, vp, C.c_bool, C.c_float, C.POINTER(EnvFns), i64]),
         "wholegraph_embedding_get_optimizer_state_names": (C.POINTER(C.c_char_p), [vp]),
         "wholegraph_embedding_get_optimizer_state": (vp, [vp, C.c_char_p]),
+        "wholegraph_b200_embedding_get_cache_tensors": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
+                                                                   C.POINTER(C.c_int)]),
         "wholegraph_embedding_writeback_cache": (C.c_int, [vp, i64]),
         "wholegraph_embedding_drop_all_cache": (C.c_int, [vp, i64]),
         "wholegraph_load_from_file": (C.c_int, [vp, sz, sz, sz, C.POINTER(C.c_char_p), C.c_int, C.c_int]),
@@ -363,6 +365,36 @@ def create_embedding(desc: TensorDescription, comm, memory_type, memory_location
                                             int(memory_location), cache_policy, part, user_defined_sms,
                                             round_robin_size), "wholegraph_create_embedding")
     return e
+
+
+def create_cache_policy(cache_comm, memory_type, memory_location, access_type, ratio: float) -> C.c_void_p:
+    """A set-associative cache in front of an embedding: `ratio` of the table's rows have a line."""
+    p = C.c_void_p()
+    check(lib().wholegraph_create_embedding_cache_policy(C.byref(p), cache_comm, int(memory_type),
+                                                         int(memory_location), int(access_type), ratio),
+          "wholegraph_create_embedding_cache_policy")
+    return p
+
+
+def destroy_cache_policy(policy) -> None:
+    check(lib().wholegraph_destroy_embedding_cache_policy(policy), "wholegraph_destroy_embedding_cache_policy")
+
+
+def embedding_writeback_all_cache(e, stream_int: int = 0) -> None:
+    check(lib().wholegraph_embedding_writeback_cache(e, stream_int), "wholegraph_embedding_writeback_cache")
+
+
+def embedding_drop_all_cache(e, stream_int: int = 0) -> None:
+    check(lib().wholegraph_embedding_drop_all_cache(e, stream_int), "wholegraph_embedding_drop_all_cache")
+
+
+def embedding_cache_tensors(e):
+    """(tags, lfu, lines, set coverage) of a cached embedding; the tensors belong to the embedding."""
+    tags, lfu, lines, cov = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_int()
+    check(lib().wholegraph_b200_embedding_get_cache_tensors(e, C.byref(tags), C.byref(lfu), C.byref(lines),
+                                                            C.byref(cov)),
+          "wholegraph_b200_embedding_get_cache_tensors")
+    return tags, lfu, lines, cov.value
 
 
 def destroy_embedding(e) -> None:

@@ -4,6 +4,7 @@
 // Reference behaviour: cpp/src/wholegraph/embedding.cpp (allocate :77-134, gradient apply
 // :136-314, state creation :316-420, C API :886-1110) and embedding_optimizer.cpp (parameter
 // names and defaults :159-180, :286-297, :385-400; state names and initial values :179-211).
+#include <cmath>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -11,11 +12,13 @@
 #include <vector>
 
 #include <wholegraph/embedding.h>
+#include <wholegraph/wholegraph_b200.h>
 #include <wholegraph/wholegraph_tensor_op.h>
 
 #include "common.hpp"
 #include "env.hpp"
 #include "handle.hpp"
+#include "kernels/cache.hpp"
 #include "kernels/row_copy.hpp"
 #include "kernels/sparse_optimizer.hpp"
 #include "ops.hpp"
@@ -37,12 +40,31 @@ struct wholegraph_embedding_optimizer_ {
   float weight_decay = 0.f, epsilon = 1e-8f, beta1 = 0.9f, beta2 = 0.999f, adam_w = 0.f, alpha = 0.99f;
 };
 
+// A set-associative cache in front of an embedding table (reference: embedding_cache.hpp:64-74,
+// embedding_cache.cpp:78-150): per set 32 tags, 32 LFU words and 32 lines, sharded like the rows
+// they cover, plus this rank's exact access counters.
+struct embedding_cache {
+  int coverage               = 32;
+  wholegraph_tensor_t tags   = nullptr;  // int16 [sets, 32]
+  wholegraph_tensor_t lfu    = nullptr;  // int16 [sets, 32]
+  wholegraph_tensor_t lines  = nullptr;  // table dtype [sets * 32, padded dim]
+  int64_t* access_count      = nullptr;  // device, one counter per local row
+  ~embedding_cache()
+  {
+    if (tags) wholegraph_destroy_tensor(tags);
+    if (lfu) wholegraph_destroy_tensor(lfu);
+    if (lines) wholegraph_destroy_tensor(lines);
+    if (access_count) cudaFree(access_count);
+  }
+};
+
 struct wholegraph_embedding_ {
   wholegraph_comm_t comm            = nullptr;
   wholegraph_dtype_t dtype          = WHOLEGRAPH_DT_UNKNOWN;
   wholegraph_tensor_t allocated     = nullptr;  // [rows, padded dim], owns the handle
   wholegraph_tensor_t user          = nullptr;  // [rows, dim] view
   wholegraph_embedding_cache_policy_t cache_policy = nullptr;
+  std::unique_ptr<embedding_cache> cache;
   int gather_sms                    = -1;
   int round_robin_size              = 0;
   int64_t dim = 0, padded_dim = 0;
@@ -77,6 +99,157 @@ local_rows_view local_view_of(wholegraph_tensor_t t)
   const int me    = h->comm->world_rank;
   return {h->local_ptr, static_cast<int64_t>(h->part_sizes[me] / eb),
           static_cast<int64_t>(h->part_offsets[me] / eb)};
+}
+
+// Rows of one cache set for a cache ratio: round(32 / ratio), at most 16384 (the 14-bit row
+// field of a tag).  Reference: embedding_cache.cpp:47-60.
+int coverage_of(float cache_ratio)
+{
+  const long c = std::lround(static_cast<double>(kCacheSetSize) / cache_ratio);
+  return static_cast<int>(std::min<long>(std::max<long>(c, kCacheSetSize), kCacheMaxCoverage));
+}
+
+// This rank's part of the cache and of the table behind it.
+cache_view local_cache_of(const wholegraph_embedding_* e)
+{
+  cache_view v;
+  if (e == nullptr || !e->cache) return v;
+  auto wl        = local_view_of(e->allocated);
+  v.tags         = static_cast<uint16_t*>(local_view_of(e->cache->tags).ptr);
+  v.lfu          = static_cast<uint16_t*>(local_view_of(e->cache->lfu).ptr);
+  v.lines        = static_cast<char*>(local_view_of(e->cache->lines).ptr);
+  v.access_count = e->cache->access_count;
+  v.raw_rows     = static_cast<char*>(wl.ptr);
+  v.first_row    = wl.start;
+  v.rows         = wl.rows;
+  v.coverage     = e->cache->coverage;
+  v.line_bytes   = e->padded_dim * static_cast<int64_t>(wholegraph_dtype_get_element_size(e->dtype));
+  return v;
+}
+
+// True when every rank can read every cache line and every table row through its own mapping,
+// so that a gather needs no exchange of rows.
+bool cache_is_mapped(const wholegraph_embedding_* e)
+{
+  auto mapped = [](wholegraph_tensor_t t) {
+    wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(t);
+    return h->type == WHOLEGRAPH_MT_CONTINUOUS && h->global_base != nullptr;
+  };
+  return mapped(e->allocated) && mapped(e->cache->tags) && mapped(e->cache->lfu) && mapped(e->cache->lines);
+}
+
+// The whole cache and table seen through the CONTINUOUS mappings (lookup only).
+cache_view global_cache_of(const wholegraph_embedding_* e)
+{
+  cache_view v   = local_cache_of(e);
+  auto base      = [](wholegraph_tensor_t t) { return wholegraph_tensor_get_memory_handle(t)->global_base; };
+  v.tags         = static_cast<uint16_t*>(base(e->cache->tags));
+  v.lfu          = static_cast<uint16_t*>(base(e->cache->lfu));
+  v.lines        = static_cast<char*>(base(e->cache->lines));
+  v.access_count = nullptr;
+  v.raw_rows     = static_cast<char*>(base(e->allocated));
+  v.first_row    = 0;
+  v.rows         = e->allocated->desc.sizes[0];
+  return v;
+}
+
+// Cache arrays for a table whose shards are whole sets.
+wholegraph_error_code_t create_cache(wholegraph_embedding_* e)
+{
+  auto* policy = e->cache_policy;
+  std::unique_ptr<embedding_cache> c(new embedding_cache());
+  c->coverage = coverage_of(policy->cache_ratio);
+  const int W = e->comm->world_size;
+  std::vector<size_t> rows_of(W), sets_of(W), lines_of(W);
+  WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_tensor_get_entry_partition_sizes(rows_of.data(), e->allocated));
+  int64_t sets = 0;
+  for (int r = 0; r < W; r++) {
+    if (rows_of[r] == 0 || rows_of[r] % c->coverage != 0) {
+      WGB_ERROR("with a cache every rank must hold a positive multiple of %d rows, rank %d holds %zu",
+                c->coverage, r, rows_of[r]);
+      return WHOLEGRAPH_INVALID_VALUE;
+    }
+    sets_of[r]  = rows_of[r] / c->coverage;
+    lines_of[r] = sets_of[r] * kCacheSetSize;
+    sets += static_cast<int64_t>(sets_of[r]);
+  }
+  wholegraph_tensor_description_t d;
+  wholegraph_initialize_tensor_desc(&d);
+  d.dim = 2, d.dtype = WHOLEGRAPH_DT_INT16;
+  d.sizes[0] = sets, d.sizes[1] = kCacheSetSize, d.strides[0] = kCacheSetSize, d.strides[1] = 1;
+  WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_create_tensor(&c->tags, &d, policy->cache_comm, policy->memory_type,
+                                                       policy->memory_location, sets_of.data()));
+  WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_create_tensor(&c->lfu, &d, policy->cache_comm, policy->memory_type,
+                                                       policy->memory_location, sets_of.data()));
+  d.dtype    = e->dtype;
+  d.sizes[0] = sets * kCacheSetSize, d.sizes[1] = e->padded_dim, d.strides[0] = e->padded_dim;
+  WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_create_tensor(&c->lines, &d, policy->cache_comm, policy->memory_type,
+                                                       policy->memory_location, lines_of.data()));
+  const int me       = e->comm->world_rank;
+  const size_t local = rows_of[me];
+  WGB_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&c->access_count), local * sizeof(int64_t)));
+  WGB_CUDA_CHECK(cudaMemset(c->access_count, 0, local * sizeof(int64_t)));
+  // Empty cache: no valid tag, zero counts.
+  WGB_CUDA_CHECK(cudaMemset(local_view_of(c->tags).ptr, 0, sets_of[me] * kCacheSetSize * sizeof(uint16_t)));
+  WGB_CUDA_CHECK(cudaMemset(local_view_of(c->lfu).ptr, 0, sets_of[me] * kCacheSetSize * sizeof(uint16_t)));
+  WGB_CUDA_CHECK(cudaDeviceSynchronize());
+  e->comm->barrier();
+  e->cache = std::move(c);
+  return WHOLEGRAPH_SUCCESS;
+}
+
+// Forward gather through the cache.
+void cached_gather(wholegraph_embedding_* e, wholegraph_tensor_t indices, wholegraph_tensor_t output,
+                   bool adjust_cache, wholegraph_env_func_t* env, cudaStream_t stream)
+{
+  auto* id = wholegraph_tensor_get_tensor_description(indices);
+  WGB_EXPECTS(id->dim == 1 && id->strides[0] == 1, "indices must be a dense 1-D tensor");
+  WGB_EXPECTS(id->dtype == WHOLEGRAPH_DT_INT || id->dtype == WHOLEGRAPH_DT_INT64,
+              "indices must be int32 or int64");
+  wholegraph_matrix_description_t od, tab;
+  WGB_EXPECTS(wholegraph_convert_tensor_desc_to_matrix(&od, wholegraph_tensor_get_tensor_description(output)),
+              "output must be a 2-D tensor");
+  WGB_EXPECTS(wholegraph_convert_tensor_desc_to_matrix(&tab, wholegraph_tensor_get_tensor_description(e->user)),
+              "bad embedding tensor");
+  WGB_EXPECTS(od.sizes[0] == id->sizes[0], "%ld output rows for %ld indices", (long)od.sizes[0],
+              (long)id->sizes[0]);
+  WGB_EXPECTS(od.sizes[1] == e->dim, "output rows have %ld elements, the embedding %ld", (long)od.sizes[1],
+              (long)e->dim);
+  const int64_t n       = id->sizes[0];
+  const bool ids_are_64 = id->dtype == WHOLEGRAPH_DT_INT64;
+  const void* ids       = wholegraph_tensor_get_data_pointer(indices);
+  void* out             = wholegraph_tensor_get_data_pointer(output);
+  wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(e->allocated);
+  auto* comm            = e->comm;
+  const cache_view mine = local_cache_of(e);
+  if (comm->world_size == 1 || !cache_is_mapped(e)) {
+    // Owners look their cache up for the ids routed to them and serve the rows.
+    gather_distributed(h, tab, ids, ids_are_64, n, out, od, env, stream, e->gather_sms, &mine, adjust_cache);
+    return;
+  }
+  // Cache and table are mapped everywhere: only the LFU update needs the ids at their owners.
+  if (adjust_cache) {
+    auto first_row = entry_offsets_of(h, wholegraph_dtype_get_element_size(e->dtype) * e->padded_dim);
+    exchange_plan plan(env);
+    plan.build(ids, ids_are_64, n, first_row, comm, stream);
+    temp_buffer ws(env);
+    if (plan.total_recv > 0)
+      cache_update(plan.recv_ids, true, plan.total_recv, mine,
+                   ws.device_bytes(cache_update_workspace_bytes(plan.total_recv)), stream);
+    // Peers read these lines next.
+    WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
+    comm->barrier();
+  }
+  if (n == 0) return;
+  temp_buffer address_buf(env);
+  auto* addr = static_cast<int64_t*>(address_buf.device(n, WHOLEGRAPH_DT_INT64));
+  cache_lookup(ids, ids_are_64, n, global_cache_of(e), false, addr, stream);
+  row_copy_args g;
+  g.src_dt = tab.dtype, g.src_stride = tab.stride, g.src_offset = tab.storage_offset;
+  g.src_select = ROW_BY_ADDRESS, g.indices = addr, g.indices_are_64 = true;
+  g.dst = out, g.dst_dt = od.dtype, g.dst_stride = od.stride, g.dst_offset = od.storage_offset;
+  g.dim = e->dim, g.count = n, g.sm_hint = e->gather_sms;
+  launch_row_copy(g, stream);
 }
 
 void destroy_states(wholegraph_embedding_* e)
@@ -114,7 +287,7 @@ wholegraph_error_code_t create_states(wholegraph_embedding_* e)
     sd.strides[0] = sd.sizes[1];
     sd.strides[1] = 1;
     WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_create_embedding(&e->state_embedding, &sd, e->comm, h->type,
-                                                            h->location, nullptr, partition.data()));
+                                                            h->location, e->cache_policy, partition.data()));
     wholegraph_tensor_t st = wholegraph_embedding_get_embedding_tensor(e->state_embedding);
     for (size_t k = 0; k < per_element.size(); k++) {
       int64_t starts[2] = {0, static_cast<int64_t>(k) * e->padded_dim};
@@ -152,7 +325,7 @@ wholegraph_error_code_t create_states(wholegraph_embedding_* e)
 
 // Backward step on already-mapped ids.
 void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, wholegraph_tensor_t grads,
-                    float lr, wholegraph_env_func_t* env, cudaStream_t stream)
+                    bool adjust_cache, float lr, wholegraph_env_func_t* env, cudaStream_t stream)
 {
   WGB_EXPECTS(e->optimizer != nullptr, "the embedding has no optimizer");
   auto* id = wholegraph_tensor_get_tensor_description(indices);
@@ -197,11 +370,26 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   a.hyper.alpha        = o->alpha;
   a.hyper.adam_w       = o->adam_w > 0.5f;
 
+  // With caches the update reads and writes a row's current copy: its line (marked modified)
+  // when it has one.  An LFU update with the ids this rank owns may come first.
+  a.weight_cache = local_cache_of(e);
+  a.state_cache  = local_cache_of(e->state_embedding);
+  temp_buffer cache_ws(env);
+  auto adjust = [&](const void* owned_ids, bool are_64, int64_t count) {
+    if (!adjust_cache || count == 0) return;
+    for (const cache_view* c : {&a.weight_cache, &a.state_cache}) {
+      if (c->tags == nullptr) continue;
+      cache_update(owned_ids, are_64, count, *c, cache_ws.device_bytes(cache_update_workspace_bytes(count)),
+                   stream);
+    }
+  };
+
   temp_buffer ws(env);
   if (W == 1) {
     if (n == 0) return;
     a.ids = ids, a.ids_are_64 = ids_are_64, a.count = n;
     a.grads = g, a.grad_stride = gd->strides[0];
+    adjust(ids, ids_are_64, n);
     sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(n, wl.rows, e->dim)), stream);
     return;
   }
@@ -239,6 +427,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   if (plan.total_recv == 0) return;
   a.ids = plan.recv_ids, a.ids_are_64 = true, a.count = plan.total_recv;
   a.grads = reinterpret_cast<const float*>(recv), a.grad_stride = e->dim;
+  adjust(plan.recv_ids, true, plan.total_recv);
   sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(plan.total_recv, wl.rows, e->dim)), stream);
 }
 
@@ -368,8 +557,14 @@ wholegraph_error_code_t wholegraph_create_embedding(
     WGB_ERROR("wholegraph_create_embedding: the description must be a 2-D matrix");
     return WHOLEGRAPH_INVALID_INPUT;
   }
-  if (cache_policy != nullptr) {
-    WGB_ERROR("cached embeddings are not available in this build");
+  if (cache_policy != nullptr && cache_policy->cache_comm != comm) {
+    // A cache on a smaller communicator than the table (every node caching the whole table for
+    // itself) is not built.
+    WGB_ERROR("a cache must be on the communicator of its embedding");
+    return WHOLEGRAPH_NOT_IMPLEMENTED;
+  }
+  if (cache_policy != nullptr && cache_policy->memory_location != WHOLEGRAPH_ML_DEVICE) {
+    WGB_ERROR("a cache must be in device memory");
     return WHOLEGRAPH_NOT_IMPLEMENTED;
   }
   WGB_API_BEGIN
@@ -381,6 +576,7 @@ wholegraph_error_code_t wholegraph_create_embedding(
   e->comm             = comm;
   e->dtype            = md.dtype;
   e->round_robin_size = round_robin_size;
+  e->cache_policy     = cache_policy;
   e->gather_sms       = (user_defined_sms >= 1 && user_defined_sms <= 1568) ? user_defined_sms : -1;
   if (user_defined_sms != -1 && e->gather_sms == -1)
     WGB_WARN("user_defined_sms=%d is outside 1..1568 and is ignored", user_defined_sms);
@@ -392,6 +588,11 @@ wholegraph_error_code_t wholegraph_create_embedding(
     if (extra > round_robin_size) extra = round_robin_size;
     const int64_t per = rows / (static_cast<int64_t>(W) * round_robin_size) * round_robin_size + extra;
     rows              = per * W;
+  }
+  if (cache_policy != nullptr && embedding_entry_partition == nullptr) {
+    // Shards of whole cache sets (reference: embedding.cpp:77-98 pads the same way).
+    const int64_t unit = static_cast<int64_t>(comm->world_size) * coverage_of(cache_policy->cache_ratio);
+    rows               = (rows + unit - 1) / unit * unit;
   }
   e->dim        = md.sizes[1];
   e->padded_dim = padded_dim_of(e->dim, wholegraph_dtype_get_element_size(md.dtype));
@@ -408,7 +609,9 @@ wholegraph_error_code_t wholegraph_create_embedding(
   int64_t starts[2] = {0, 0};
   int64_t ends[2]   = {rows, e->dim};
   auto rc           = wholegraph_tensor_get_subtensor(e->allocated, starts, ends, &e->user);
+  if (rc == WHOLEGRAPH_SUCCESS && cache_policy != nullptr) rc = create_cache(e.get());
   if (rc != WHOLEGRAPH_SUCCESS) {
+    if (e->user) wholegraph_destroy_tensor(e->user);
     wholegraph_destroy_tensor(e->allocated);
     return rc;
   }
@@ -422,6 +625,7 @@ wholegraph_error_code_t wholegraph_destroy_embedding(wholegraph_embedding_t e)
   if (e == nullptr) return WHOLEGRAPH_INVALID_INPUT;
   WGB_API_BEGIN
   destroy_states(e);
+  e->cache.reset();
   if (e->user) wholegraph_destroy_tensor(e->user);
   if (e->allocated) wholegraph_destroy_tensor(e->allocated);
   delete e;
@@ -465,11 +669,14 @@ wholegraph_error_code_t wholegraph_embedding_gather(wholegraph_embedding_t e,
                                                       wholegraph_env_func_t* p_env_fns,
                                                       int64_t stream_int)
 {
-  (void)adjust_cache;
   if (e == nullptr || indices == nullptr || output == nullptr) return WHOLEGRAPH_INVALID_INPUT;
   WGB_API_BEGIN
   auto stream = reinterpret_cast<cudaStream_t>(stream_int);
   return with_mapped_indices(e, indices, p_env_fns, stream, [&](wholegraph_tensor_t ids) {
+    if (e->cache) {
+      cached_gather(e, ids, output, adjust_cache, p_env_fns, stream);
+      return WHOLEGRAPH_SUCCESS;
+    }
     return wholegraph_gather(e->user, ids, output, p_env_fns, stream, e->gather_sms);
   });
   WGB_API_END("wholegraph_embedding_gather")
@@ -483,12 +690,11 @@ wholegraph_error_code_t wholegraph_embedding_gather_gradient_apply(wholegraph_em
                                                                      wholegraph_env_func_t* p_env_fns,
                                                                      int64_t stream_int)
 {
-  (void)adjust_cache;
   if (e == nullptr || indices == nullptr || grads == nullptr) return WHOLEGRAPH_INVALID_INPUT;
   WGB_API_BEGIN
   auto stream = reinterpret_cast<cudaStream_t>(stream_int);
   return with_mapped_indices(e, indices, p_env_fns, stream, [&](wholegraph_tensor_t ids) {
-    gradient_apply(e, ids, grads, lr, p_env_fns, stream);
+    gradient_apply(e, ids, grads, adjust_cache, lr, p_env_fns, stream);
     return WHOLEGRAPH_SUCCESS;
   });
   WGB_API_END("wholegraph_embedding_gather_gradient_apply")
@@ -508,15 +714,51 @@ wholegraph_tensor_t wholegraph_embedding_get_optimizer_state(wholegraph_embeddin
   return it == e->state_views.end() ? nullptr : it->second;
 }
 
-wholegraph_error_code_t wholegraph_embedding_writeback_cache(wholegraph_embedding_t e, int64_t)
+wholegraph_error_code_t wholegraph_b200_embedding_get_cache_tensors(wholegraph_embedding_t e,
+                                                                      wholegraph_tensor_t* tags,
+                                                                      wholegraph_tensor_t* lfu,
+                                                                      wholegraph_tensor_t* lines,
+                                                                      int* set_coverage)
 {
-  // Without a cache there is nothing to write back.
-  return e == nullptr ? WHOLEGRAPH_INVALID_INPUT : WHOLEGRAPH_SUCCESS;
+  if (e == nullptr || !e->cache) return WHOLEGRAPH_INVALID_INPUT;
+  if (tags) *tags = e->cache->tags;
+  if (lfu) *lfu = e->cache->lfu;
+  if (lines) *lines = e->cache->lines;
+  if (set_coverage) *set_coverage = e->cache->coverage;
+  return WHOLEGRAPH_SUCCESS;
 }
 
-wholegraph_error_code_t wholegraph_embedding_drop_all_cache(wholegraph_embedding_t e, int64_t)
+}  // extern "C"
+
+namespace {
+// Modified lines of the embedding and of its optimizer state go back to their tables; every rank
+// waits until all have finished, so that the tables can be read or saved right after.
+wholegraph_error_code_t flush_cache(wholegraph_embedding_t e, bool drop, int64_t stream_int)
 {
-  return e == nullptr ? WHOLEGRAPH_INVALID_INPUT : WHOLEGRAPH_SUCCESS;
+  if (e == nullptr) return WHOLEGRAPH_INVALID_INPUT;
+  if (!e->cache) return WHOLEGRAPH_SUCCESS;  // nothing to write back
+  WGB_API_BEGIN
+  auto stream = reinterpret_cast<cudaStream_t>(stream_int);
+  cache_writeback(local_cache_of(e), drop, stream);
+  if (e->state_embedding != nullptr && e->state_embedding->cache)
+    cache_writeback(local_cache_of(e->state_embedding), drop, stream);
+  WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
+  e->comm->barrier();
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_embedding_writeback_cache")
+}
+}  // namespace
+
+extern "C" {
+
+wholegraph_error_code_t wholegraph_embedding_writeback_cache(wholegraph_embedding_t e, int64_t stream_int)
+{
+  return flush_cache(e, false, stream_int);
+}
+
+wholegraph_error_code_t wholegraph_embedding_drop_all_cache(wholegraph_embedding_t e, int64_t stream_int)
+{
+  return flush_cache(e, true, stream_int);
 }
 
 }  // extern "C"

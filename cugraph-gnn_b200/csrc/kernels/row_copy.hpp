@@ -16,6 +16,9 @@ enum row_select_t : int {
   ROW_SEQUENTIAL = 0,  // row i
   ROW_BY_INDEX   = 1,  // row indices[i]          (the table side)
   ROW_BY_POSITION = 2, // row positions[i]        (reorder through a permutation)
+  ROW_BY_ADDRESS  = 3, // indices[i] is the int64 byte address of the row itself (negative: skip);
+                       // the side's pointer is ignored, its offset is added, its stride only
+                       // states the rows' alignment
 };
 
 // A table whose rows live behind one base pointer per rank (CHUNKED memory).  When

@@ -41,8 +41,10 @@ int row_copy_vector_elements(const row_copy_args& a)
     int64_t addr = chunked_side ? 0 : reinterpret_cast<intptr_t>(p);
     return addr / es + off;
   };
-  const bool src_chunked = a.chunks.ranks > 0 && a.src_select == ROW_BY_INDEX;
-  const bool dst_chunked = a.chunks.ranks > 0 && a.dst_select == ROW_BY_INDEX;
+  // A side addressed row by row (chunked table or explicit addresses) contributes only its
+  // offset and stride: its rows are allocations or lines aligned to their stride.
+  const bool src_chunked = (a.chunks.ranks > 0 && a.src_select == ROW_BY_INDEX) || a.src_select == ROW_BY_ADDRESS;
+  const bool dst_chunked = (a.chunks.ranks > 0 && a.dst_select == ROW_BY_INDEX) || a.dst_select == ROW_BY_ADDRESS;
   const int64_t s0       = first_elt(a.src, es_src, a.src_offset, src_chunked);
   const int64_t d0       = first_elt(a.dst, es_dst, a.dst_offset, dst_chunked);
   for (; epv > 1; epv /= 2) {
@@ -63,7 +65,15 @@ void launch_row_copy(const row_copy_args& a, cudaStream_t stream)
               "row copy between dtype %d and dtype %d is not supported", (int)a.src_dt,
               (int)a.dst_dt);
   if (a.count == 0 || a.dim == 0) return;
-  const bool need_index = a.src_select == ROW_BY_INDEX || a.dst_select == ROW_BY_INDEX;
+  if (a.src_select == ROW_BY_ADDRESS || a.dst_select == ROW_BY_ADDRESS) {
+    // Rows named by address: same kernel, with "row number" = address, stride 1 byte and the
+    // storage offset as base.  Alignment comes from the stated stride and offset.
+    WGB_EXPECTS(a.indices != nullptr && a.indices_are_64 && a.chunks.ranks == 0 &&
+                  !(a.src_select == ROW_BY_ADDRESS && a.dst_select == ROW_BY_ADDRESS),
+                "bad by-address row copy");
+  }
+  const bool need_index = a.src_select == ROW_BY_INDEX || a.dst_select == ROW_BY_INDEX ||
+                          a.src_select == ROW_BY_ADDRESS || a.dst_select == ROW_BY_ADDRESS;
   const bool need_pos   = a.src_select == ROW_BY_POSITION || a.dst_select == ROW_BY_POSITION;
   WGB_EXPECTS(!need_index || a.indices != nullptr, "row copy by index without indices");
   WGB_EXPECTS(!need_pos || a.positions != nullptr, "row copy by position without positions");
@@ -98,6 +108,16 @@ void launch_row_copy(const row_copy_args& a, cudaStream_t stream)
   p.lanes_per_row      = lpr;
   p.src_select         = a.src_select;
   p.dst_select         = a.dst_select;
+  if (a.src_select == ROW_BY_ADDRESS) {
+    p.src              = reinterpret_cast<const char*>(a.src_offset * es_src);
+    p.src_stride_bytes = 1;
+    p.src_select       = ROW_BY_INDEX;
+  }
+  if (a.dst_select == ROW_BY_ADDRESS) {
+    p.dst              = reinterpret_cast<char*>(a.dst_offset * es_dst);
+    p.dst_stride_bytes = 1;
+    p.dst_select       = ROW_BY_INDEX;
+  }
   p.indices_are_64     = a.indices_are_64 ? 1 : 0;
   p.chunks             = a.chunks;
   p.segments           = a.segments;

@@ -129,7 +129,26 @@ struct apply_params {
   int32_t* slot_run;      // per slot: long run it belongs to
   int32_t* slot_block;    // per slot: block number inside the run
   float* partial;         // [slots, dim] block sums
+  cache_view weight_cache;
+  cache_view state_cache;
 };
+
+// Where row `row` of this rank's shard lives right now: its cache line (marked modified) when
+// it is cached, `table_row` otherwise.  Warp-wide: lane l inspects line l of the row's set.
+__device__ __forceinline__ char* current_copy(const cache_view& c, uint32_t row, int lane, char* table_row)
+{
+  if (c.tags == nullptr) return table_row;
+  const int64_t set  = row / c.coverage;
+  const uint16_t r   = static_cast<uint16_t>(row - set * c.coverage);
+  uint16_t* tag_ptr  = c.tags + set * kCacheSetSize + lane;
+  const uint16_t tag = *tag_ptr;
+  const bool hit     = (tag & kTagValid) != 0 && (tag & kTagRowMask) == r;
+  const unsigned m   = __ballot_sync(0xffffffffu, hit);
+  if (m == 0) return table_row;
+  const int line = __ffs(m) - 1;
+  if (lane == line) *tag_ptr = tag | kTagModified;
+  return c.lines + (set * kCacheSetSize + line) * c.line_bytes;
+}
 
 // One element of the update.  g is the summed gradient; w, s0, s1 are read-modify-write.
 template <int OPT>
@@ -279,6 +298,9 @@ __global__ void __launch_bounds__(kThreads) apply_kernel(const apply_params p)
     step_betas<OPT>(p, row, lane, beta1t, beta2t);
     W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
     float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
+    w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, row, lane, reinterpret_cast<char*>(w_row)));
+    if (s_row != nullptr)
+      s_row = reinterpret_cast<float*>(current_copy(p.state_cache, row, lane, reinterpret_cast<char*>(s_row)));
     for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
       float acc[VEC];
       sum_rows<VEC>(p, first, last, c, acc);
@@ -329,6 +351,9 @@ __global__ void __launch_bounds__(kThreads) apply_long_kernel(const apply_params
     step_betas<OPT>(p, row, lane, beta1t, beta2t);
     W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
     float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
+    w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, row, lane, reinterpret_cast<char*>(w_row)));
+    if (s_row != nullptr)
+      s_row = reinterpret_cast<float*>(current_copy(p.state_cache, row, lane, reinterpret_cast<char*>(s_row)));
     for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
       float acc[VEC];
 #pragma unroll
@@ -517,6 +542,7 @@ void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stre
   p.weights = a.weights, p.weight_stride = a.weight_stride;
   p.state = a.state, p.state_stride = a.state_stride, p.v_offset = a.v_offset, p.beta12t = a.beta12t;
   p.h = a.hyper;
+  p.weight_cache = a.weight_cache, p.state_cache = a.state_cache;
   p.long_count = counters + 1, p.slot_count = counters + 2;
   p.long_first = reinterpret_cast<int32_t*>(ws + l.long_first);
   p.long_len   = reinterpret_cast<int32_t*>(ws + l.long_len);

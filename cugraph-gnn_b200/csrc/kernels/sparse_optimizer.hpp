@@ -13,6 +13,8 @@
 #include <wholegraph/wholegraph_b200.h>
 #include <wholegraph/tensor_description.h>
 
+#include "cache.hpp"
+
 namespace wgb {
 
 struct optimizer_hyper {
@@ -46,6 +48,12 @@ struct sparse_apply_args {
   int64_t state_stride = 0;
   int64_t v_offset     = 0;        // Lazy Adam: v lives v_offset elements after m in a state row
   float* beta12t       = nullptr;  // Lazy Adam: [local_rows, 2] running beta1^t, beta2^t per row
+  // Optional caches in front of the weight rows and the state rows (tags == nullptr: none).  A row
+  // that is cached is updated in its cache line, which is marked modified; the table row is left
+  // alone until the line is written back (reference: optimizer_get_ptr_from_cache,
+  // embedding_optimizer_func.cu:140-164).
+  cache_view weight_cache;
+  cache_view state_cache;
   optimizer_hyper hyper;
 };
 

@@ -19,6 +19,7 @@
 #include "common.hpp"
 #include "env.hpp"
 #include "handle.hpp"
+#include "kernels/cache.hpp"
 #include "kernels/partition.hpp"
 #include "kernels/row_copy.hpp"
 #include "kernels/unique_ids.hpp"
@@ -238,11 +239,13 @@ struct table_side {
   chunked_table chunks;
 };
 
+}  // namespace
+
 // ---- distributed gather ----------------------------------------------------------------------
 void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_description_t& tab,
                         const void* ids, bool ids_are_64, int64_t n, void* out,
                         const wholegraph_matrix_description_t& od, wholegraph_env_func_t* env,
-                        cudaStream_t stream, int sms)
+                        cudaStream_t stream, int sms, const cache_view* cache, bool adjust_cache)
 {
   WGB_EXPECTS(tab.storage_offset >= 0 && tab.storage_offset + tab.sizes[1] <= tab.stride,
               "distributed gather needs storage_offset + dim <= stride");
@@ -261,9 +264,17 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
   g.src_select = ROW_BY_INDEX;
   g.dst_dt = od.dtype, g.dim = dim, g.indices_are_64 = true, g.sm_hint = sms;
 
+  temp_buffer cache_ws(env), address_buf(env);
   if (W == 1) {
     g.dst = out, g.dst_stride = od.stride, g.dst_offset = od.storage_offset;
     g.indices = ids, g.indices_are_64 = ids_are_64, g.count = n;
+    if (cache != nullptr) {
+      if (adjust_cache)
+        cache_update(ids, ids_are_64, n, *cache, cache_ws.device_bytes(cache_update_workspace_bytes(n)), stream);
+      auto* addr = static_cast<int64_t*>(address_buf.device(n, WHOLEGRAPH_DT_INT64));
+      cache_lookup(ids, ids_are_64, n, *cache, false, addr, stream);
+      g.src_select = ROW_BY_ADDRESS, g.indices = addr, g.indices_are_64 = true;
+    }
     launch_row_copy(g, stream);
     return;
   }
@@ -276,7 +287,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
     const char* e = getenv("WG_GATHER_DEDUP");
     return e == nullptr || e[0] != '0';
   }();
-  const bool dedup = dedup_wanted && unique_supported(n, first_row[W]);
+  const bool dedup = cache == nullptr && dedup_wanted && unique_supported(n, first_row[W]);
   plan.build(ids, ids_are_64, n, first_row, comm, stream, dedup);
   timer.mark(dedup ? "unique+counts+ids" : "partition+counts+ids");
 
@@ -320,12 +331,25 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
   char* serve = static_cast<char*>(serve_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
   char* recv  = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
 
+  // With a cache, every id this rank serves (its own requests included: they are part of
+  // recv_ids) is resolved to the address of the row's current copy first.
+  const int64_t* serve_index = plan.recv_ids;
+  if (cache != nullptr && plan.total_recv > 0) {
+    if (adjust_cache)
+      cache_update(plan.recv_ids, true, plan.total_recv, *cache,
+                   cache_ws.device_bytes(cache_update_workspace_bytes(plan.total_recv)), stream);
+    auto* addr = static_cast<int64_t*>(address_buf.device(plan.total_recv, WHOLEGRAPH_DT_INT64));
+    cache_lookup(plan.recv_ids, true, plan.total_recv, *cache, false, addr, stream);
+    serve_index  = addr;
+    g.src_select = ROW_BY_ADDRESS;
+  }
+
   // Step 0: rows this rank owns go straight from the shard to their final output rows.
   {
     row_copy_args a = g;
     a.dst = out, a.dst_stride = od.stride, a.dst_offset = od.storage_offset;
     a.dst_select = ROW_BY_POSITION;
-    a.indices    = plan.sorted_ids + plan.send_displs[me];
+    a.indices    = cache != nullptr ? serve_index + plan.recv_displs[me] : plan.sorted_ids + plan.send_displs[me];
     a.positions  = plan.positions + plan.send_displs[me];
     a.count      = plan.send_counts[me];
     launch_row_copy(a, stream);
@@ -339,7 +363,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
 
   row_copy_args serve_rows = g;  // rows other ranks asked for -> serve buffer, in their order
   serve_rows.dst = serve, serve_rows.dst_stride = dim, serve_rows.dst_offset = 0;
-  serve_rows.dst_select = ROW_SEQUENTIAL, serve_rows.indices = plan.recv_ids;
+  serve_rows.dst_select = ROW_SEQUENTIAL, serve_rows.indices = serve_index;
 
   pipelined_exchange(
     comm, plan.recv_counts, plan.recv_displs, plan.send_counts, plan.send_displs, serve, recv, row_b, stream,
@@ -355,6 +379,8 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
     });
   timer.mark("exchange+reorder");
 }
+
+namespace {
 
 // ---- distributed scatter ---------------------------------------------------------------------
 void scatter_distributed(const void* in, const wholegraph_matrix_description_t& id_,

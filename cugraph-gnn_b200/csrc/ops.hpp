@@ -7,6 +7,8 @@
 #include <functional>
 #include <vector>
 
+#include <wholegraph/tensor_description.h>
+
 #include "comm.hpp"
 #include "env.hpp"
 #include "handle.hpp"
@@ -58,6 +60,17 @@ void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_
                         size_t row_bytes, cudaStream_t stream,
                         const std::function<void(const list_segments&)>& pack,
                         const std::function<void(const list_segments&)>& unpack);
+
+struct cache_view;
+// Gather rows of a DISTRIBUTED table (descriptor `tab` over handle `h`) into `out`.  With
+// `cache` (this rank's part of a set-associative cache in front of its shard) owners serve each
+// row from its cache line when it has one, after an optional LFU update with the ids they
+// received (`adjust_cache`); duplicates are then routed as they are, because the update counts
+// them.
+void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_description_t& tab, const void* ids,
+                        bool ids_are_64, int64_t n, void* out, const wholegraph_matrix_description_t& od,
+                        wholegraph_env_func_t* env, cudaStream_t stream, int sms,
+                        const cache_view* cache = nullptr, bool adjust_cache = false);
 
 // First row of every rank's shard (world + 1 entries) for rows of `entry_bytes` bytes.
 std::vector<int64_t> entry_offsets_of(wholegraph_handle_* h, size_t entry_bytes);

@@ -8,8 +8,10 @@
 
 #include <stdint.h>
 
+#include <wholegraph/embedding.h>
 #include <wholegraph/env_func_ptrs.h>
 #include <wholegraph/wholegraph.h>
+#include <wholegraph/wholegraph_tensor.h>
 
 /*
  * Duplicate-gradient reduction of wholegraph_embedding_gather_gradient_apply: gradients of equal
@@ -103,6 +105,18 @@ wholegraph_error_code_t wholegraph_b200_partition_by_owner_no_alloc(const void* 
                                                                       int64_t* counts,
                                                                       int64_t* starts,
                                                                       void* stream);
+
+/* The arrays of a cached embedding, for inspection and tests (no counterpart in the reference's
+ * C API; its cache object keeps them private, cpp/src/wholegraph/embedding_cache.hpp:64-74):
+ * tags and LFU words as int16 [sets, 32] tensors, the cache lines as a [sets * 32, padded dim]
+ * tensor of the table's dtype, and the number of consecutive table rows one set covers.  A tag is
+ * valid (bit 14) | modified (bit 15) | row number inside the set (bits 0-13).  The tensors belong
+ * to the embedding.  WHOLEGRAPH_INVALID_INPUT for an embedding without a cache. */
+wholegraph_error_code_t wholegraph_b200_embedding_get_cache_tensors(wholegraph_embedding_t embedding,
+                                                                      wholegraph_tensor_t* tags,
+                                                                      wholegraph_tensor_t* lfu,
+                                                                      wholegraph_tensor_t* lines,
+                                                                      int* set_coverage);
 
 /* Number of kernels this library has launched in this process since load. */
 unsigned long long wholegraph_b200_kernel_launch_count();

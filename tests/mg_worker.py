@@ -128,10 +128,16 @@ def main():
         wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
         wgb.destroy_wholegraph_tensor(t)
 
-    def check_gradient_apply(mem_type, opt_type, opt_code, rows, dim, n, steps, table_dtype=torch.float32):
-        print(f"rank {rank}: gradient apply {mem_type.name} opt={opt_code} rows={rows} dim={dim}", flush=True)
+    def check_gradient_apply(mem_type, opt_type, opt_code, rows, dim, n, steps, table_dtype=torch.float32,
+                             cache_type=None):
+        print(f"rank {rank}: gradient apply {mem_type.name} opt={opt_code} rows={rows} dim={dim} "
+              f"cache={cache_type}", flush=True)
+        policy = None
+        if cache_type is not None:   # rows must already be a multiple of world * 128
+            policy = wgb.create_cache_policy(comm, cache_type, ML.MlDevice, wgb.WholeGraphAccessType.AtReadWrite,
+                                             0.25)
         emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(tu.TORCH_TO_WG[table_dtype])), comm,
-                                   mem_type, ML.MlDevice)
+                                   mem_type, ML.MlDevice, cache_policy=policy)
         opt = wgb.create_optimizer(opt_type, weight_decay=0.01)
         wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
         table = wgb.embedding_tensor(emb)
@@ -157,7 +163,7 @@ def main():
                 all_grads.append(rng.uniform(-1, 1, size=(n, dim)).astype(np.float32))
             d_ids, d_grads = torch.from_numpy(all_ids[rank]).cuda(), torch.from_numpy(all_grads[rank]).cuda()
             wi, wg = tu.wrap_torch_tensor(d_ids), tu.wrap_torch_tensor(d_grads)
-            wgb.EmbeddingGatherGradientApply(emb, wi, wg, False, 0.01, env, tu.current_stream_int())
+            wgb.EmbeddingGatherGradientApply(emb, wi, wg, policy is not None, 0.01, env, tu.current_stream_int())
             torch.cuda.synchronize()
             wgb.destroy_wholegraph_tensor(wi)
             wgb.destroy_wholegraph_tensor(wg)
@@ -166,6 +172,22 @@ def main():
             uniq, sums = orc.dedup_gradients(np.concatenate(all_ids), np.concatenate(all_grads))
             orc.optimizer_apply(opt_code, uniq, sums, w_host, lr=0.01, state=state, v_offset=padded, beta12t=beta,
                                 weight_decay=0.01, weights_bf16=(table_dtype == torch.bfloat16))
+        if policy is not None:
+            # forward gathers through the cache see the trained rows (with and without an LFU
+            # update), then the write-back puts them into the tables
+            for step, adjust in enumerate((True, False, True)):
+                ids = np.random.default_rng(77 * step + rank).integers(0, rows // 4, size=4_000).astype(np.int64)
+                d_ids = torch.from_numpy(ids).cuda()
+                out = torch.empty((len(ids), dim), dtype=table_dtype, device="cuda")
+                wi, wo = tu.wrap_torch_tensor(d_ids), tu.wrap_torch_tensor(out)
+                wgb.EmbeddingGatherForward(emb, wi, wo, adjust, env, tu.current_stream_int())
+                torch.cuda.synchronize()
+                wgb.destroy_wholegraph_tensor(wi)
+                wgb.destroy_wholegraph_tensor(wo)
+                assert np.array_equal(to_host(out).view(w_host.dtype), w_host[ids]), \
+                    f"cached gather {step} differs on rank {rank}"
+                wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            wgb.embedding_writeback_all_cache(emb)
         got = torch.empty((hi - lo, dim), dtype=table_dtype, device="cuda")
         tu.gather(table, mine, got, env)
         torch.cuda.synchronize()
@@ -178,7 +200,19 @@ def main():
         wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
         wgb.destroy_embedding(emb)
         wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
+        if policy is not None:
+            wgb.destroy_cache_policy(policy)
 
+    if scenario == "cache":
+        OT = wgb.WholeGraphOptimizerType
+        rows = 128 * 8 * 5
+        check_gradient_apply(MT.MtContinuous, OT.OptLazyAdam, 2, rows, 64, 4_000, 3, cache_type=MT.MtContinuous)
+        check_gradient_apply(MT.MtDistributed, OT.OptSgd, 1, rows, 33, 3_000, 3, cache_type=MT.MtDistributed)
+        check_gradient_apply(MT.MtChunked, OT.OptAdaGrad, 4, 2 * rows, 100, 3_000, 2, torch.bfloat16,
+                             cache_type=MT.MtChunked)
+        wgb.destroy_communicator(comm)
+        print(f"rank {rank} ok", flush=True)
+        return
     if scenario == "optimizer":
         OT = wgb.WholeGraphOptimizerType
         check_gradient_apply(MT.MtDistributed, OT.OptLazyAdam, 2, 20_011, 64, 6_000, 3)

@@ -1,0 +1,188 @@
+"""GPU tests of the cached embedding path through the C ABI: forward gather through a
+set-associative cache with LFU updates, write-back, drop, and training through the cache.
+
+The reference tests the same properties
+(cpp/tests/wholegraph_tensor_ops/wholegraph_embedding_tests.cu, cached cases of
+wholegraph_embedding_gradient_apply_tests.cu:798-1007): a cached embedding must return exactly
+what the uncached table holds, whatever the cache keeps, and after a write-back the table must
+hold what an uncached run would have produced.  The cache policy itself (which rows get the 32
+lines of a set) is checked against a model of the rule this library states: exact access
+counts, highest counts cached, cached rows win ties, then lower row numbers."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+VALID, MODIFIED, ROW_MASK = 1 << 14, 1 << 15, (1 << 14) - 1
+
+
+@pytest.fixture(scope="module")
+def comm(gpu, wgb):
+    c = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+    yield c
+    wgb.destroy_communicator(c)
+
+
+def _zipf_like(rng, rows, n):
+    """Skewed ids: a hot tenth of the table takes most accesses."""
+    hot = rng.integers(0, max(rows // 10, 1), size=n)
+    cold = rng.integers(0, rows, size=n)
+    return np.where(rng.random(n) < 0.8, hot, cold)
+
+
+def _make(gpu, wgb, comm, rows, dim, torch_dtype, ratio, mem_type=None, cache_type=None):
+    MT, ML, AT, DT = (wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphAccessType,
+                      wgb.WholeGraphDataType)
+    mem_type = mem_type or MT.MtContinuous
+    cache_type = cache_type or MT.MtContinuous
+    policy = wgb.create_cache_policy(comm, cache_type, ML.MlDevice, AT.AtReadWrite, ratio)
+    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(gpu.TORCH_TO_WG[torch_dtype])), comm,
+                               mem_type, ML.MlDevice, cache_policy=policy)
+    return emb, policy
+
+
+def _read_tensor(gpu, torch, t, rows, cols, dtype):
+    ids = torch.arange(rows, device="cuda", dtype=torch.int64)
+    out = torch.empty((rows, cols), dtype=dtype, device="cuda")
+    gpu.gather(t, ids, out)
+    torch.cuda.synchronize()
+    return out
+
+
+def _forward(gpu, wgb, torch, emb, ids_np, dim, dtype, adjust):
+    d_ids = torch.from_numpy(ids_np).cuda()
+    out = torch.empty((len(ids_np), dim), dtype=dtype, device="cuda")
+    wi, wo = gpu.wrap_torch_tensor(d_ids), gpu.wrap_torch_tensor(out)
+    wgb.EmbeddingGatherForward(emb, wi, wo, adjust, wgb.cached_env_fns(), gpu.current_stream_int())
+    torch.cuda.synchronize()
+    wgb.destroy_wholegraph_tensor(wi)
+    wgb.destroy_wholegraph_tensor(wo)
+    return out
+
+
+class PolicyModel:
+    """The stated update rule, per set: counters are exact; after a batch the cached rows of every
+    touched set are the 32 with the highest counters among (cached U accessed), cached rows first
+    on ties, then lower row numbers; rows that stay keep their line."""
+
+    def __init__(self, rows, coverage):
+        self.count = np.zeros(rows, dtype=np.int64)
+        self.coverage = coverage
+        self.cached = {}          # set -> {row in set: line}
+
+    def update(self, ids):
+        uniq, cnt = np.unique(ids, return_counts=True)
+        self.count[uniq] += cnt
+        for s in np.unique(uniq // self.coverage):
+            lines = self.cached.setdefault(int(s), {})
+            touched = uniq[uniq // self.coverage == s] - s * self.coverage
+            cand = [(-(self.count[s * self.coverage + r] * 2 + 1), r) for r in lines]
+            cand += [(-(self.count[s * self.coverage + r] * 2), int(r)) for r in touched if int(r) not in lines]
+            keep = [r for _, r in sorted(cand)[:32]]
+            free = sorted(set(range(32)) - {lines[r] for r in keep if r in lines})
+            new = {r: lines[r] for r in keep if r in lines}
+            for r in keep:                      # new rows take freed lines in priority order
+                if r not in lines:
+                    new[r] = free.pop(0)
+            self.cached[int(s)] = new
+
+
+@pytest.mark.parametrize("dtype_name,dim", [("f32", 32), ("f32", 13), ("f16", 64), ("bf16", 100)])
+@pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
+def test_cached_gather_returns_the_table_and_follows_the_policy(gpu, wgb, comm, dtype_name, dim, idx_dtype):
+    import torch
+    dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[dtype_name]
+    rows, ratio = 5000, 0.25                       # coverage 128 -> 40 sets of 32 lines, 5120 rows
+    rng = np.random.default_rng(dim * 7 + idx_dtype().itemsize)
+    emb, policy = _make(gpu, wgb, comm, rows, dim, dtype, ratio)
+    table = wgb.embedding_tensor(emb)
+    tags_t, lfu_t, lines_t, coverage = wgb.embedding_cache_tensors(emb)
+    assert coverage == 128
+    padded_rows = -(-rows // coverage) * coverage
+    init = torch.from_numpy(rng.uniform(-1, 1, size=(padded_rows, dim)).astype(np.float32)).cuda().to(dtype)
+    gpu.scatter(init, torch.arange(padded_rows, device="cuda", dtype=torch.int64), table)
+    torch.cuda.synchronize()
+    model = PolicyModel(padded_rows, coverage)
+    sets = padded_rows // coverage
+
+    for step in range(6):
+        ids = _zipf_like(rng, rows, 3000).astype(idx_dtype)
+        adjust = step != 3                          # one step only reads
+        out = _forward(gpu, wgb, torch, emb, ids, dim, dtype, adjust)
+        assert torch.equal(out, init[torch.from_numpy(ids.astype(np.int64)).cuda()]), f"step {step}"
+        if adjust:
+            model.update(ids.astype(np.int64))
+        tags = _read_tensor(gpu, torch, tags_t, sets, 32, torch.int16).cpu().numpy().view(np.uint16)
+        for s in range(sets):
+            got = {int(t & ROW_MASK): line for line, t in enumerate(tags[s]) if t & VALID}
+            assert got == model.cached.get(s, {}), f"step {step} set {s}"
+        assert not (tags & MODIFIED).any()
+        # every valid line holds its row
+        esz = init.element_size()
+        pad = -(-dim // (16 // esz)) * (16 // esz)
+        lines = _read_tensor(gpu, torch, lines_t, sets * 32, pad, dtype)
+        s_idx, l_idx = np.nonzero(tags & VALID)
+        src_rows = s_idx * coverage + (tags[s_idx, l_idx] & ROW_MASK)
+        assert torch.equal(lines[torch.from_numpy(s_idx * 32 + l_idx).cuda(), :dim],
+                           init[torch.from_numpy(src_rows.astype(np.int64)).cuda()])
+    # hits must have happened: the hot rows are cached
+    assert sum(len(v) for v in model.cached.values()) > 32
+    wgb.embedding_drop_all_cache(emb)
+    tags = _read_tensor(gpu, torch, tags_t, sets, 32, torch.int16).cpu().numpy()
+    assert not tags.any()
+    ids = _zipf_like(rng, rows, 500).astype(idx_dtype)
+    out = _forward(gpu, wgb, torch, emb, ids, dim, dtype, False)
+    assert torch.equal(out, init[torch.from_numpy(ids.astype(np.int64)).cuda()])
+    wgb.destroy_embedding(emb)
+    wgb.destroy_cache_policy(policy)
+
+
+def test_cache_ratio_bounds_and_coverage(gpu, wgb, comm):
+    import torch
+    MT, ML, AT = wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphAccessType
+    p = C.c_void_p()
+    for bad in (1.5, 1.0 / 1024):
+        rc = wgb.lib().wholegraph_create_embedding_cache_policy(C.byref(p), comm, int(MT.MtContinuous),
+                                                                int(ML.MlDevice), int(AT.AtReadWrite), bad)
+        assert rc == 7                               # WHOLEGRAPH_INVALID_VALUE
+    for ratio, want in ((1.0, 32), (0.5, 64), (0.1, 320), (1.0 / 512, 16384)):
+        emb, policy = _make(gpu, wgb, comm, 100, 8, torch.float32, ratio)
+        assert wgb.embedding_cache_tensors(emb)[3] == want
+        d = wgb.lib().wholegraph_tensor_get_tensor_description(wgb.embedding_tensor(emb)).contents
+        assert d.sizes[0] == -(-100 // want) * want  # rows padded to whole sets
+        wgb.destroy_embedding(emb)
+        wgb.destroy_cache_policy(policy)
+
+
+def test_a_full_cache_serves_every_row_from_its_lines(gpu, wgb, comm):
+    """ratio 1: every row has a line, so after one pass over all ids every later gather hits, and
+    overwriting the table behind the cache must not change what a cached gather returns."""
+    import torch
+    rows, dim = 1024, 16
+    emb, policy = _make(gpu, wgb, comm, rows, dim, torch.float32, 1.0)
+    table = wgb.embedding_tensor(emb)
+    all_ids = torch.arange(rows, device="cuda", dtype=torch.int64)
+    init = torch.arange(rows * dim, device="cuda", dtype=torch.float32).reshape(rows, dim)
+    gpu.scatter(init, all_ids, table)
+    _forward(gpu, wgb, torch, emb, np.arange(rows, dtype=np.int64), dim, torch.float32, True)
+    gpu.scatter(torch.zeros_like(init), all_ids, table)          # behind the cache's back
+    torch.cuda.synchronize()
+    out = _forward(gpu, wgb, torch, emb, np.arange(rows, dtype=np.int64)[::-1].copy(), dim, torch.float32, False)
+    assert torch.equal(out, init.flip(0))
+    # nothing is modified, so a write-back leaves the zeros in the table
+    wgb.embedding_writeback_all_cache(emb)
+    assert not _read_tensor(gpu, torch, table, rows, dim, torch.float32).any()
+    wgb.destroy_embedding(emb)
+    wgb.destroy_cache_policy(policy)
+
+
+@pytest.mark.parametrize("opt_name,params", [("sgd", {"weight_decay": 0.1}), ("adam", {}),
+                                             ("adagrad", {}), ("rmsprop", {"alpha": 0.9})])
+@pytest.mark.parametrize("table_dtype,dim", [("f32", 32), ("f32", 129), ("bf16", 64)])
+def test_training_through_the_cache_matches_the_oracle(gpu, wgb, orc, comm, opt_name, params, table_dtype, dim):
+    from test_optimizer_gpu import _run
+    MT = wgb.WholeGraphMemoryType
+    _run(gpu, wgb, orc, comm, opt_name, rows=3000, dim=dim, table_dtype=table_dtype, idx_dtype=np.int64,
+         steps=5, n=2000, params=params, mem_type=MT.MtContinuous, cache_ratio=0.125)

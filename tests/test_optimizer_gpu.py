@@ -35,14 +35,20 @@ def _read_all(gpu, torch, wg_tensor, rows, dim, dtype):
     return out
 
 
-def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps, n, params, mem_type, block=0):
+def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps, n, params, mem_type, block=0,
+         cache_ratio=None):
     import torch
     DT, MT, ML = wgb.WholeGraphDataType, wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation
     tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[table_dtype]
     wg_dt = gpu.TORCH_TO_WG[tdt]
     rng = np.random.default_rng(hash((opt_name, dim, table_dtype)) % (2 ** 31))
     env = wgb.cached_env_fns()
-    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(wg_dt)), comm, mem_type, ML.MlDevice)
+    policy = None
+    if cache_ratio is not None:   # train through a set-associative cache in front of table and state
+        policy = wgb.create_cache_policy(comm, mem_type, ML.MlDevice, wgb.WholeGraphAccessType.AtReadWrite,
+                                         cache_ratio)
+    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(wg_dt)), comm, mem_type, ML.MlDevice,
+                               cache_policy=policy)
     opt = wgb.create_optimizer(wgb.WholeGraphOptimizerType(OPTS[opt_name]), **params)
     wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
     table = wgb.embedding_tensor(emb)
@@ -66,7 +72,8 @@ def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps
         grads = rng.uniform(-1, 1, size=(n, dim)).astype(np.float32)
         d_idx, d_grads = torch.from_numpy(idx).cuda(), torch.from_numpy(grads).cuda()  # keep them alive
         wi, wg = gpu.wrap_torch_tensor(d_idx), gpu.wrap_torch_tensor(d_grads)
-        wgb.EmbeddingGatherGradientApply(emb, wi, wg, False, lr, env, gpu.current_stream_int())
+        wgb.EmbeddingGatherGradientApply(emb, wi, wg, policy is not None and step != 2, lr, env,
+                                         gpu.current_stream_int())
         torch.cuda.synchronize()
         wgb.destroy_wholegraph_tensor(wi)
         wgb.destroy_wholegraph_tensor(wg)
@@ -79,6 +86,24 @@ def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps
                             beta1=params.get("beta1", 0.9), beta2=params.get("beta2", 0.999),
                             alpha=params.get("alpha", 0.99), adam_w=params.get("adam_w", 0.0) > 0.5)
 
+    if policy is not None:
+        # a gather through the cache sees the trained rows before anything is written back ...
+        ids = torch.arange(rows, device="cuda", dtype=torch.int64)
+        out = torch.empty((rows, dim), dtype=tdt, device="cuda")
+        wi, wo = gpu.wrap_torch_tensor(ids), gpu.wrap_torch_tensor(out)
+        wgb.EmbeddingGatherForward(emb, wi, wo, False, env, gpu.current_stream_int())
+        torch.cuda.synchronize()
+        wgb.destroy_wholegraph_tensor(wi)
+        wgb.destroy_wholegraph_tensor(wo)
+        assert np.array_equal(_host_bits(torch, out).view(w_host.dtype), w_host), "cached gather differs"
+        tags = wgb.embedding_cache_tensors(emb)[0]
+        sets = wgb.lib().wholegraph_tensor_get_tensor_description(tags).contents.sizes[0]
+        bits = _read_all(gpu, torch, tags, sets, 32, torch.int16).cpu().numpy().view(np.uint16)
+        assert (bits & 0x8000).any(), "training never touched a cache line"
+        # ... and the tables hold them after the write-back
+        wgb.embedding_writeback_all_cache(emb)
+        bits = _read_all(gpu, torch, tags, sets, 32, torch.int16).cpu().numpy().view(np.uint16)
+        assert not (bits & 0x8000).any()
     got_w = _host_bits(torch, _read_all(gpu, torch, table, rows, dim, tdt))
     assert np.array_equal(got_w.view(w_host.dtype), w_host), "weights differ from the oracle"
     names = wgb.embedding_state_names(emb)
@@ -91,6 +116,8 @@ def _run(gpu, wgb, orc, comm, opt_name, rows, dim, table_dtype, idx_dtype, steps
         assert np.array_equal(b, beta_host)
     wgb.destroy_embedding(emb)
     wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
+    if policy is not None:
+        wgb.destroy_cache_policy(policy)
 
 
 @pytest.mark.parametrize("opt_name,params", [("sgd", {}), ("sgd", {"weight_decay": 0.1}),
