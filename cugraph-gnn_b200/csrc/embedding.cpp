@@ -5,6 +5,7 @@
 // :136-314, state creation :316-420, C API :886-1110) and embedding_optimizer.cpp (parameter
 // names and defaults :159-180, :286-297, :385-400; state names and initial values :179-211).
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <memory>
@@ -394,36 +395,65 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     return;
   }
 
-  // Route every gradient row to the owner of its id: same W-step pipeline as a distributed
-  // scatter, with fp32 rows on the wire.
   wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(e->allocated);
   auto first_row        = entry_offsets_of(h, wholegraph_dtype_get_element_size(e->dtype) * e->padded_dim);
+  const size_t row_b    = static_cast<size_t>(e->dim) * sizeof(float);
   exchange_plan plan(env);
-  plan.build(ids, ids_are_64, n, first_row, comm, stream);
-  const size_t row_b = static_cast<size_t>(e->dim) * sizeof(float);
-  temp_buffer send_buf(env), recv_buf(env);
-  char* send = static_cast<char*>(send_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
-  char* recv = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
-  row_copy_args pack;
-  pack.src = g, pack.src_dt = WHOLEGRAPH_DT_FLOAT, pack.src_stride = gd->strides[0];
-  pack.src_select = ROW_BY_POSITION;
-  pack.dst_dt = WHOLEGRAPH_DT_FLOAT, pack.dst_stride = e->dim, pack.dim = e->dim;
-  {  // own rows go straight into their slot of the receive buffer
-    row_copy_args s0 = pack;
-    s0.dst           = recv + plan.recv_displs[me] * row_b;
-    s0.positions     = plan.positions + plan.send_displs[me];
-    s0.count         = plan.send_counts[me];
-    launch_row_copy(s0, stream);
+  temp_buffer send_buf(env), recv_buf(env), uid_buf(env), counts_buf(env), presum_ws(env);
+  char* recv = nullptr;
+
+  // WG_GRADIENT_PRESUM=0 routes every gradient row, as the reference does.  By default each rank
+  // first adds up its own duplicates, so that an id crosses the wire at most once per rank and a
+  // hot row does not flood its owner; the owner then adds the per-rank sums in rank order.
+  const char* presum_env = getenv("WG_GRADIENT_PRESUM");
+  const bool presum = (presum_env == nullptr || presum_env[0] != '0') &&
+                      reduce_duplicates_supported(n, first_row[W], W);
+  if (presum) {
+    int64_t* cdev = static_cast<int64_t*>(counts_buf.device(3 * W, WHOLEGRAPH_DT_INT64));
+    int64_t* uids = static_cast<int64_t*>(uid_buf.device(std::max<int64_t>(n, 1), WHOLEGRAPH_DT_INT64));
+    char* sums    = static_cast<char*>(send_buf.device_bytes(std::max<size_t>(1, n * row_b)));
+    if (n > 0) {
+      reduce_duplicates(ids, ids_are_64, n, g, gd->strides[0], e->dim, first_row.data(), W,
+                        presum_ws.device_bytes(reduce_duplicates_workspace_bytes(n, first_row[W], e->dim)), uids,
+                        reinterpret_cast<float*>(sums), cdev, cdev + W, stream);
+    } else {
+      WGB_CUDA_CHECK(cudaMemsetAsync(cdev, 0, sizeof(int64_t) * 2 * W, stream));
+    }
+    plan.build_grouped(uids, cdev, comm, stream);
+    recv = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
+    if (plan.send_counts[me] > 0)  // own rows go straight into their slot of the receive buffer
+      WGB_CUDA_CHECK(cudaMemcpyAsync(recv + plan.recv_displs[me] * row_b, sums + plan.send_displs[me] * row_b,
+                                     plan.send_counts[me] * row_b, cudaMemcpyDeviceToDevice, stream));
+    auto nothing = [](const list_segments&) {};  // rows are already where the exchange reads them
+    pipelined_exchange(comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, sums, recv,
+                       row_b, stream, nothing, nothing);
+  } else {
+    // Every gradient row goes to the owner of its id: the pipeline of a distributed scatter, with
+    // fp32 rows on the wire.
+    plan.build(ids, ids_are_64, n, first_row, comm, stream);
+    char* send = static_cast<char*>(send_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
+    recv       = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
+    row_copy_args pack;
+    pack.src = g, pack.src_dt = WHOLEGRAPH_DT_FLOAT, pack.src_stride = gd->strides[0];
+    pack.src_select = ROW_BY_POSITION;
+    pack.dst_dt = WHOLEGRAPH_DT_FLOAT, pack.dst_stride = e->dim, pack.dim = e->dim;
+    {  // own rows go straight into their slot of the receive buffer
+      row_copy_args s0 = pack;
+      s0.dst           = recv + plan.recv_displs[me] * row_b;
+      s0.positions     = plan.positions + plan.send_displs[me];
+      s0.count         = plan.send_counts[me];
+      launch_row_copy(s0, stream);
+    }
+    pack.dst = send, pack.positions = plan.positions;
+    pipelined_exchange(
+      comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, send, recv, row_b, stream,
+      [&](const list_segments& seg) {
+        row_copy_args ps = pack;
+        ps.segments = seg, ps.count = seg.total();
+        launch_row_copy(ps, stream);
+      },
+      [](const list_segments&) {});  // the update below needs every row: nothing to do per chunk
   }
-  pack.dst = send, pack.positions = plan.positions;
-  pipelined_exchange(
-    comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, send, recv, row_b, stream,
-    [&](const list_segments& seg) {
-      row_copy_args ps = pack;
-      ps.segments = seg, ps.count = seg.total();
-      launch_row_copy(ps, stream);
-    },
-    [](const list_segments&) {});  // the update below needs every row: nothing to do per chunk
   if (plan.total_recv == 0) return;
   a.ids = plan.recv_ids, a.ids_are_64 = true, a.count = plan.total_recv;
   a.grads = reinterpret_cast<const float*>(recv), a.grad_stride = e->dim;

@@ -5,9 +5,12 @@
 //                         equal ids keep their arrival order
 //   3. cub select         first element of every run of equal keys, in order (run r ends where
 //                         run r + 1 starts)
-//   4. apply_kernel       one warp per distinct row: walks its run, adds the gradient rows in
-//                         arrival order (fp32, 16-byte loads, 4 rows in flight), then reads
-//                         weights and state once, updates them and writes them back
+//   4. apply_kernel       a CTA stages the metadata of 256 runs, then one warp per distinct row
+//                         requests the first gradient row, weights and state together, adds
+//                         further duplicates in arrival order (fp32, 16-byte loads), updates
+//                         and writes back; runs longer than 256 rows are registered only
+//   5. sum_blocks_kernel  long runs: one warp per (block of 256 rows, column group)
+//   6. apply_long_kernel  long runs: block sums added in order, then the same update
 //
 // The summed gradients never go to memory (the reference writes them to a [unique, dim] fp32
 // buffer and reads them back).  Arithmetic follows the reference kernels
@@ -32,8 +35,8 @@ namespace wgb {
 namespace {
 
 constexpr int kThreads    = 256;
+constexpr int kMaxOwnerRanks = 64;
 constexpr int kDedupBlock = WHOLEGRAPH_B200_DEDUP_BLOCK;  // rows per block of a long duplicate run
-constexpr int kRowsInFlight = 8;  // gradient rows a lane requests before it starts adding
 
 __global__ void keys_kernel(const void* ids, int is64, int64_t n, int64_t local_start,
                             int64_t local_rows, uint32_t* keys, int32_t* positions)
@@ -124,6 +127,10 @@ struct apply_params {
   int32_t* long_first;    // per long run: index of its first sorted element
   int32_t* long_len;      // per long run: number of elements
   int32_t* long_slot;     // per long run: first partial-sum slot
+  float2* long_beta;      // per long run: the row's stepped beta1^t, beta2^t (Lazy Adam)
+  int32_t* long_run;      // per long run: its number among all runs (reduce-only mode)
+  int64_t* unique_ids;    // reduce-only mode: id of every run, ascending
+  int64_t id_base;        // reduce-only mode: id of key 0
   int32_t* long_count;    // number of long runs
   int32_t* slot_count;    // number of partial-sum slots handed out
   int32_t* slot_run;      // per slot: long run it belongs to
@@ -183,200 +190,301 @@ __device__ __forceinline__ void update_element(const optimizer_hyper& h, float g
   }
 }
 
-// Sum of the gradient rows of sorted elements [first, last) for columns [c, c + VEC), added one
-// after the other in that order; kRowsInFlight rows are requested before the first is added.
+// VEC gradient elements through the read-only path; nothing is read when `on` is false.
 template <int VEC>
-__device__ __forceinline__ void sum_rows(const apply_params& p, int64_t first, int64_t last, int c,
-                                         float (&acc)[VEC])
+__device__ __forceinline__ void load_grad(const float* g, bool on, float (&out)[VEC])
 {
-  {
-    const float* g0 = p.grads + static_cast<int64_t>(p.positions[first]) * p.grad_stride + c;
-    if constexpr (VEC == 4) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(g0));
-      acc[0] = v.x, acc[1] = v.y, acc[2] = v.z, acc[3] = v.w;
-    } else {
-      acc[0] = __ldg(g0);
-    }
-  }
-  for (int64_t k = first + 1; k < last; k += kRowsInFlight) {
-    float v[kRowsInFlight][VEC];
-    bool on[kRowsInFlight];
-#pragma unroll
-    for (int u = 0; u < kRowsInFlight; u++) {
-      on[u] = k + u < last;
-      if (on[u]) {
-        const float* g = p.grads + static_cast<int64_t>(p.positions[k + u]) * p.grad_stride + c;
-        if constexpr (VEC == 4) {
-          const float4 t = __ldg(reinterpret_cast<const float4*>(g));
-          v[u][0] = t.x, v[u][1] = t.y, v[u][2] = t.z, v[u][3] = t.w;
-        } else {
-          v[u][0] = __ldg(g);
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kRowsInFlight; u++) {
-      if (on[u]) {
-#pragma unroll
-        for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
-      }
-    }
+  if (!on) return;
+  if constexpr (VEC == 4) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(g));
+    out[0] = v.x, out[1] = v.y, out[2] = v.z, out[3] = v.w;
+  } else {
+    out[0] = __ldg(g);
   }
 }
 
-// Read-modify-write of weights and state for columns [c, c + VEC) of one row.
+// Weights and state of columns [c, c + VEC) of one row, held in registers between the loads
+// (issued together with the first gradient loads) and the update.
 template <int OPT, typename W, int VEC>
-__device__ __forceinline__ void update_columns(const apply_params& p, W* w_row, float* s_row, int c,
-                                               const float (&acc)[VEC], float beta1t, float beta2t)
-{
+struct row_columns {
   float w[VEC], s0[VEC], s1[VEC];
-  load_vec<W, VEC>(w_row + c, w);
-  if (OPT != WHOLEGRAPH_OPT_SGD) load_vec<float, VEC>(s_row + c, s0);
-  if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) load_vec<float, VEC>(s_row + p.v_offset + c, s1);
+  __device__ __forceinline__ void load(const apply_params& p, const W* w_row, const float* s_row, int c, bool on)
+  {
+    if (!on || OPT == WHOLEGRAPH_OPT_NONE) return;
+    load_vec<W, VEC>(w_row + c, w);
+    if (OPT != WHOLEGRAPH_OPT_SGD) load_vec<float, VEC>(s_row + c, s0);
+    if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) load_vec<float, VEC>(s_row + p.v_offset + c, s1);
+  }
+  __device__ __forceinline__ void update_and_store(const apply_params& p, W* w_row, float* s_row, int c, bool on,
+                                                   const float (&g)[VEC], float beta1t, float beta2t)
+  {
+    if (!on) return;
+    if constexpr (OPT == WHOLEGRAPH_OPT_NONE) {  // reduce only: the row of sums is the output
+      store_vec<W, VEC>(w_row + c, g);
+    } else {
 #pragma unroll
-  for (int e = 0; e < VEC; e++) update_element<OPT>(p.h, acc[e], w[e], s0[e], s1[e], beta1t, beta2t);
-  if (OPT != WHOLEGRAPH_OPT_SGD) store_vec<float, VEC>(s_row + c, s0);
-  if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) store_vec<float, VEC>(s_row + p.v_offset + c, s1);
-  store_vec<W, VEC>(w_row + c, w);
-}
-
-// Per-row running beta1^t, beta2^t of Lazy Adam: multiplied on every touch of the row.
-template <int OPT>
-__device__ __forceinline__ void step_betas(const apply_params& p, uint32_t row, int lane, float& beta1t,
-                                           float& beta2t)
-{
-  beta1t = beta2t = 0.f;
-  if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
-    beta1t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 0], p.h.beta1);
-    beta2t = __fmul_rn(p.beta12t[static_cast<int64_t>(row) * 2 + 1], p.h.beta2);
-    __syncwarp();  // every lane has read the old values before lane 0 overwrites them
-    if (lane == 0) {
-      p.beta12t[static_cast<int64_t>(row) * 2 + 0] = beta1t;
-      p.beta12t[static_cast<int64_t>(row) * 2 + 1] = beta2t;
+      for (int e = 0; e < VEC; e++) update_element<OPT>(p.h, g[e], w[e], s0[e], s1[e], beta1t, beta2t);
+      if (OPT != WHOLEGRAPH_OPT_SGD) store_vec<float, VEC>(s_row + c, s0);
+      if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) store_vec<float, VEC>(s_row + p.v_offset + c, s1);
+      store_vec<W, VEC>(w_row + c, w);
     }
   }
-}
+};
 
-// One warp per distinct row.  Runs of up to kDedupBlock duplicates are summed and applied here;
-// longer runs are only registered, with one partial-sum slot per block of kDedupBlock rows.
+constexpr int kTileRuns    = kThreads;  // runs whose metadata one CTA stages at a time, one per thread
+constexpr int kApplyFlight = 4;         // duplicate rows a lane requests (for two column groups) before adding
+
+// Distinct rows with at most kDedupBlock duplicates: summed and applied here.  Longer runs are
+// only registered, with one partial-sum slot per block of kDedupBlock rows.
+//
+// A CTA takes kTileRuns consecutive runs.  Its threads first stage, in parallel and with
+// coalesced loads, everything a run's update depends on: where the run starts and ends, its row,
+// the list position of its first gradient row and (Lazy Adam) the row's stepped beta powers.
+// Its warps then take runs from the tile one by one; with the metadata in shared memory a warp
+// can request the first gradient row, the weights and the state of up to two column groups in
+// one go, so that a run costs one memory round trip plus one per kApplyFlight further duplicates
+// (their list positions come 32 at a time from one coalesced load, handed out by shuffles).
 // VEC = 4: dim, strides and base pointers allow 16-byte accesses; VEC = 1 otherwise.
 template <int OPT, typename W, int VEC>
-__global__ void __launch_bounds__(kThreads) apply_kernel(const apply_params p)
+__global__ void __launch_bounds__(kThreads, 2) apply_kernel(const apply_params p)
 {
-  const int lane            = threadIdx.x & 31;
-  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int runs            = *p.head_count;
-  W* weights                = static_cast<W*>(p.weights);
+  __shared__ int32_t s_first[kTileRuns + 1];
+  __shared__ uint32_t s_row[kTileRuns];
+  __shared__ int32_t s_pos0[kTileRuns];  // -1: nothing to do here (foreign ids, long run)
+  __shared__ float s_beta[OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? kTileRuns : 1][2];
+  __shared__ int s_next;
+  const int lane = threadIdx.x & 31;
+  const int t    = threadIdx.x;
+  const int runs = *p.head_count;
+  W* weights     = static_cast<W*>(p.weights);
+  constexpr unsigned kFull = 0xffffffffu;
 
-  for (int64_t run = warp_global; run < runs; run += warp_stride) {
-    // Heads are in sorted order, so a run ends where the next one starts.
-    const int64_t first = p.heads[run];
-    const int64_t last  = run + 1 < runs ? p.heads[run + 1] : p.n;
-    const uint32_t row  = p.keys[first];
-    if (row == p.sentinel) continue;  // ids this rank does not own sort last
-    const int64_t len = last - first;
-    if (len > kDedupBlock) {
-      const int blocks = static_cast<int>((len + kDedupBlock - 1) / kDedupBlock);
-      int li = 0, slot = 0;
-      if (lane == 0) {
-        li               = atomicAdd(p.long_count, 1);
-        slot             = atomicAdd(p.slot_count, blocks);
-        p.long_first[li] = static_cast<int32_t>(first);
-        p.long_len[li]   = static_cast<int32_t>(len);
-        p.long_slot[li]  = slot;
-      }
-      li   = __shfl_sync(0xffffffffu, li, 0);
-      slot = __shfl_sync(0xffffffffu, slot, 0);
-      for (int b = lane; b < blocks; b += 32) {
-        p.slot_run[slot + b]   = li;
-        p.slot_block[slot + b] = b;
-      }
-      continue;
+  for (int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kTileRuns; tile0 < runs;
+       tile0 += static_cast<int64_t>(gridDim.x) * kTileRuns) {
+    __syncthreads();  // the previous tile has been consumed
+    const int64_t run = tile0 + t;
+    int32_t first     = static_cast<int32_t>(p.n);
+    uint32_t row      = p.sentinel;
+    int32_t pos0      = -1;
+    if (run < runs) {
+      first = p.heads[run];
+      row   = p.keys[first];
+      pos0  = p.positions[first];
     }
-    float beta1t, beta2t;
-    step_betas<OPT>(p, row, lane, beta1t, beta2t);
-    W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
-    float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
-    w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, row, lane, reinterpret_cast<char*>(w_row)));
-    if (s_row != nullptr)
-      s_row = reinterpret_cast<float*>(current_copy(p.state_cache, row, lane, reinterpret_cast<char*>(s_row)));
-    for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
-      float acc[VEC];
-      sum_rows<VEC>(p, first, last, c, acc);
-      update_columns<OPT, W, VEC>(p, w_row, s_row, c, acc, beta1t, beta2t);
+    s_first[t] = first;
+    if (t == 0) {
+      s_first[kTileRuns] = tile0 + kTileRuns < runs ? p.heads[tile0 + kTileRuns] : static_cast<int32_t>(p.n);
+      s_next             = 0;
+    }
+    __syncthreads();
+    if (row == p.sentinel) pos0 = -1;  // ids this rank does not own sort last
+    if (pos0 >= 0) {
+      const int len = s_first[t + 1] - first;  // heads ascend: a run ends where the next one starts
+      if (OPT == WHOLEGRAPH_OPT_NONE) p.unique_ids[run] = p.id_base + row;
+      float beta1t = 0.f, beta2t = 0.f;
+      if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
+        // per-row running beta1^t, beta2^t: multiplied on every touch of the row
+        float2* b = reinterpret_cast<float2*>(p.beta12t) + row;
+        float2 v  = *b;
+        v.x = beta1t = __fmul_rn(v.x, p.h.beta1);
+        v.y = beta2t = __fmul_rn(v.y, p.h.beta2);
+        *b           = v;
+      }
+      if (len > kDedupBlock) {
+        const int blocks  = (len + kDedupBlock - 1) / kDedupBlock;
+        const int li      = atomicAdd(p.long_count, 1);
+        const int slot    = atomicAdd(p.slot_count, blocks);
+        p.long_first[li]  = first;
+        p.long_len[li]    = len;
+        p.long_slot[li]   = slot;
+        p.long_beta[li]   = make_float2(beta1t, beta2t);
+        p.long_run[li]    = static_cast<int32_t>(run);
+        for (int b = 0; b < blocks; b++) {
+          p.slot_run[slot + b]   = li;
+          p.slot_block[slot + b] = b;
+        }
+        pos0 = -1;
+      } else if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
+        s_beta[t][0] = beta1t, s_beta[t][1] = beta2t;
+      }
+    }
+    s_row[t]  = row;
+    s_pos0[t] = pos0;
+    __syncthreads();
+
+    const int in_tile = static_cast<int>(runs - tile0 < kTileRuns ? runs - tile0 : kTileRuns);
+    for (;;) {
+      int r = 0;
+      if (lane == 0) r = atomicAdd(&s_next, 1);
+      r = __shfl_sync(kFull, r, 0);
+      if (r >= in_tile) break;
+      const int first_pos = s_pos0[r];
+      if (first_pos < 0) continue;
+      const int64_t begin = s_first[r], end = s_first[r + 1];
+      const uint32_t urow = s_row[r];
+      const float beta1t  = OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? s_beta[r][0] : 0.f;
+      const float beta2t  = OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? s_beta[r][1] : 0.f;
+      // reduce only: sums go to row <run number> of the output, which stands in for the table
+      const int64_t out_row = OPT == WHOLEGRAPH_OPT_NONE ? tile0 + r : static_cast<int64_t>(urow);
+      W* w_row     = weights + out_row * p.weight_stride;
+      float* s_rw  = p.state != nullptr ? p.state + static_cast<int64_t>(urow) * p.state_stride : nullptr;
+      w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, urow, lane, reinterpret_cast<char*>(w_row)));
+      if (s_rw != nullptr)
+        s_rw = reinterpret_cast<float*>(current_copy(p.state_cache, urow, lane, reinterpret_cast<char*>(s_rw)));
+      const float* g_first = p.grads + static_cast<int64_t>(first_pos) * p.grad_stride;
+
+      for (int cb = 0; cb < p.dim; cb += 64 * VEC) {  // two column groups per pass, warp-uniform trip count
+        const int c0 = cb + lane * VEC, c1 = c0 + 32 * VEC;
+        const bool on0 = c0 < p.dim, on1 = c1 < p.dim;
+        float acc0[VEC] = {}, acc1[VEC] = {};
+        row_columns<OPT, W, VEC> x0, x1;
+        load_grad<VEC>(g_first + c0, on0, acc0);
+        load_grad<VEC>(g_first + c1, on1, acc1);
+        x0.load(p, w_row, s_rw, c0, on0);
+        x1.load(p, w_row, s_rw, c1, on1);
+        // further duplicates, in arrival order
+        for (int64_t base = begin; end - begin > 1 && base < end; base += 32) {
+          const int chunk = static_cast<int>(end - base < 32 ? end - base : 32);
+          const int mine  = lane < chunk ? p.positions[base + lane] : 0;
+          for (int j = base == begin ? 1 : 0; j < chunk; j += kApplyFlight) {
+            float v0[kApplyFlight][VEC], v1[kApplyFlight][VEC];
+#pragma unroll
+            for (int u = 0; u < kApplyFlight; u++) {
+              const int pos   = __shfl_sync(kFull, mine, (j + u) & 31);
+              const bool live = j + u < chunk;
+              const float* g  = p.grads + static_cast<int64_t>(pos) * p.grad_stride;
+              load_grad<VEC>(g + c0, live && on0, v0[u]);
+              load_grad<VEC>(g + c1, live && on1, v1[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < kApplyFlight; u++) {
+              if (j + u < chunk) {
+#pragma unroll
+                for (int e = 0; e < VEC; e++) {
+                  acc0[e] = __fadd_rn(acc0[e], v0[u][e]);
+                  acc1[e] = __fadd_rn(acc1[e], v1[u][e]);
+                }
+              }
+            }
+          }
+        }
+        x0.update_and_store(p, w_row, s_rw, c0, on0, acc0, beta1t, beta2t);
+        x1.update_and_store(p, w_row, s_rw, c1, on1, acc1, beta1t, beta2t);
+      }
     }
   }
 }
 
-// One warp per partial-sum slot: block b of a long run, rows [b * kDedupBlock, (b + 1) * kDedupBlock)
-// of the run, added in order.
+constexpr int kBlockFlight = 8;  // gradient rows in flight per lane while a block is summed
+
+// One warp per (partial-sum slot, group of 32 * VEC columns): block b of a long run, rows
+// [b * kDedupBlock, (b + 1) * kDedupBlock) of the run, added in order.  List positions are read 32
+// at a time, one coalesced load ahead of their use.
 template <int VEC>
-__global__ void __launch_bounds__(kThreads) sum_blocks_kernel(const apply_params p)
+__global__ void __launch_bounds__(kThreads, 3) sum_blocks_kernel(const apply_params p)
 {
+  constexpr unsigned kFull  = 0xffffffffu;
   const int lane            = threadIdx.x & 31;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int slots           = *p.slot_count;
-  for (int64_t s = warp_global; s < slots; s += warp_stride) {
+  const int groups          = (p.dim + 32 * VEC - 1) / (32 * VEC);
+  const int64_t units       = static_cast<int64_t>(*p.slot_count) * groups;
+  for (int64_t unit = warp_global; unit < units; unit += warp_stride) {
+    const int64_t s     = unit / groups;
+    const int c         = static_cast<int>(unit - s * groups) * 32 * VEC + lane * VEC;
+    const bool on       = c < p.dim;
     const int li        = p.slot_run[s];
     const int64_t begin = p.long_first[li];
     const int64_t end   = begin + p.long_len[li];
     const int64_t first = begin + static_cast<int64_t>(p.slot_block[s]) * kDedupBlock;
     const int64_t last  = first + kDedupBlock < end ? first + kDedupBlock : end;
-    float* out          = p.partial + s * p.dim;
-    for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
-      float acc[VEC];
-      sum_rows<VEC>(p, first, last, c, acc);
+    float acc[VEC]      = {};
+    int next_pos        = first + lane < last ? p.positions[first + lane] : 0;
+    for (int64_t base = first; base < last; base += 32) {
+      const int chunk = static_cast<int>(last - base < 32 ? last - base : 32);
+      const int mine  = next_pos;
+      if (base + 32 < last) next_pos = base + 32 + lane < last ? p.positions[base + 32 + lane] : 0;
+      for (int j = 0; j < chunk; j += kBlockFlight) {
+        float v[kBlockFlight][VEC];
 #pragma unroll
-      for (int e = 0; e < VEC; e++) out[c + e] = acc[e];
+        for (int u = 0; u < kBlockFlight; u++) {
+          const int pos = __shfl_sync(kFull, mine, (j + u) & 31);
+          load_grad<VEC>(p.grads + static_cast<int64_t>(pos) * p.grad_stride + c, on && j + u < chunk, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kBlockFlight; u++) {
+          if (j + u < chunk) {
+            if (base == first && j + u == 0) {  // the first row starts the sum
+#pragma unroll
+              for (int e = 0; e < VEC; e++) acc[e] = v[u][e];
+            } else {
+#pragma unroll
+              for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
+            }
+          }
+        }
+      }
+    }
+    if (on) {
+      float* out = p.partial + s * p.dim + c;
+#pragma unroll
+      for (int e = 0; e < VEC; e++) out[e] = acc[e];
     }
   }
 }
 
-// One warp per long run: adds its block sums in block order and applies the optimizer.
+constexpr int kPartialFlight = 16;  // block sums in flight per lane while a long run is finished
+
+// One warp per (long run, group of 32 * VEC columns): adds the run's block sums in block order and
+// applies the optimizer to its columns.
 template <int OPT, typename W, int VEC>
-__global__ void __launch_bounds__(kThreads) apply_long_kernel(const apply_params p)
+__global__ void __launch_bounds__(kThreads, 2) apply_long_kernel(const apply_params p)
 {
   const int lane            = threadIdx.x & 31;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int runs            = *p.long_count;
+  const int groups          = (p.dim + 32 * VEC - 1) / (32 * VEC);
+  const int64_t units       = static_cast<int64_t>(*p.long_count) * groups;
   W* weights                = static_cast<W*>(p.weights);
-  for (int64_t li = warp_global; li < runs; li += warp_stride) {
+  for (int64_t unit = warp_global; unit < units; unit += warp_stride) {
+    const int64_t li   = unit / groups;
+    const int c        = static_cast<int>(unit - li * groups) * 32 * VEC + lane * VEC;
+    const bool on      = c < p.dim;
     const uint32_t row = p.keys[p.long_first[li]];
     const int blocks   = (p.long_len[li] + kDedupBlock - 1) / kDedupBlock;
-    const float* part  = p.partial + static_cast<int64_t>(p.long_slot[li]) * p.dim;
-    float beta1t, beta2t;
-    step_betas<OPT>(p, row, lane, beta1t, beta2t);
-    W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
+    const float* part  = p.partial + static_cast<int64_t>(p.long_slot[li]) * p.dim + c;
+    const float2 beta  = p.long_beta[li];
+    const int64_t out_row = OPT == WHOLEGRAPH_OPT_NONE ? p.long_run[li] : static_cast<int64_t>(row);
+    W* w_row     = weights + out_row * p.weight_stride;
     float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
     w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, row, lane, reinterpret_cast<char*>(w_row)));
     if (s_row != nullptr)
       s_row = reinterpret_cast<float*>(current_copy(p.state_cache, row, lane, reinterpret_cast<char*>(s_row)));
-    for (int c = lane * VEC; c < p.dim; c += 32 * VEC) {
-      float acc[VEC];
+    row_columns<OPT, W, VEC> x;
+    x.load(p, w_row, s_row, c, on);
+    float acc[VEC] = {};
+    if (on) {
 #pragma unroll
-      for (int e = 0; e < VEC; e++) acc[e] = part[c + e];
-      for (int b = 1; b < blocks; b += kRowsInFlight) {
-        float v[kRowsInFlight][VEC];
+      for (int e = 0; e < VEC; e++) acc[e] = part[e];
+      for (int b = 1; b < blocks; b += kPartialFlight) {
+        float v[kPartialFlight][VEC];
 #pragma unroll
-        for (int u = 0; u < kRowsInFlight; u++) {
+        for (int u = 0; u < kPartialFlight; u++) {
           if (b + u < blocks) {
 #pragma unroll
-            for (int e = 0; e < VEC; e++) v[u][e] = part[static_cast<int64_t>(b + u) * p.dim + c + e];
+            for (int e = 0; e < VEC; e++) v[u][e] = part[static_cast<int64_t>(b + u) * p.dim + e];
           }
         }
 #pragma unroll
-        for (int u = 0; u < kRowsInFlight; u++) {
+        for (int u = 0; u < kPartialFlight; u++) {
           if (b + u < blocks) {
 #pragma unroll
             for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
           }
         }
       }
-      update_columns<OPT, W, VEC>(p, w_row, s_row, c, acc, beta1t, beta2t);
     }
+    x.update_and_store(p, w_row, s_row, c, on, acc, beta.x, beta.y);
   }
 }
 
@@ -398,7 +506,7 @@ __global__ void round_robin_kernel(const I* ids, I* out, int64_t n, int world, i
 
 struct workspace_layout {
   size_t keys_in, keys_out, pos_in, pos_out, heads, counters, cub, total;
-  size_t long_first, long_len, long_slot, slot_run, slot_block, partial;
+  size_t long_first, long_len, long_slot, long_beta, long_run, slot_run, slot_block, partial;
   size_t cub_bytes, select_bytes;
 };
 
@@ -427,6 +535,8 @@ workspace_layout layout_for(int64_t n, int64_t local_rows, int64_t dim)
   l.long_first = off, off += align(max_long * 4);
   l.long_len   = off, off += align(max_long * 4);
   l.long_slot  = off, off += align(max_long * 4);
+  l.long_beta  = off, off += align(max_long * 8);
+  l.long_run   = off, off += align(max_long * 4);
   l.slot_run   = off, off += align(max_slots * 4);
   l.slot_block = off, off += align(max_slots * 4);
   l.partial    = off, off += align(max_slots * static_cast<size_t>(std::max<int64_t>(dim, 1)) * 4);
@@ -448,7 +558,7 @@ template <int OPT, typename W>
 void launch_apply(const apply_params& p, bool vec4, int ctas, cudaStream_t stream)
 {
   // Long runs are rare and their number is only known on the device: fixed modest grids.
-  const int long_ctas = std::min(ctas, 148 * 4);
+  const int long_ctas = 148 * 4;
   if (vec4) {
     apply_kernel<OPT, W, 4><<<ctas, kThreads, 0, stream>>>(p);
     sum_blocks_kernel<4><<<long_ctas, kThreads, 0, stream>>>(p);
@@ -464,6 +574,9 @@ template <typename W>
 void launch_apply_opt(const apply_params& p, bool vec4, int ctas, cudaStream_t stream)
 {
   switch (p.h.type) {
+    case WHOLEGRAPH_OPT_NONE:
+      if constexpr (sizeof(W) == 4) launch_apply<WHOLEGRAPH_OPT_NONE, W>(p, vec4, ctas, stream);
+      break;
     case WHOLEGRAPH_OPT_SGD: launch_apply<WHOLEGRAPH_OPT_SGD, W>(p, vec4, ctas, stream); break;
     case WHOLEGRAPH_OPT_LAZY_ADAM: launch_apply<WHOLEGRAPH_OPT_LAZY_ADAM, W>(p, vec4, ctas, stream); break;
     case WHOLEGRAPH_OPT_ADAGRAD: launch_apply<WHOLEGRAPH_OPT_ADAGRAD, W>(p, vec4, ctas, stream); break;
@@ -503,6 +616,123 @@ void round_robin_remap(const void* ids, void* out, bool ids_are_64, int64_t coun
   WGB_LAUNCH_CHECK(stream);
 }
 
+namespace {
+
+// Steps 1-3 of every pass: keys, stable sort, ordered run heads.  Fills the grouping fields of
+// `p` and its long-run scratch pointers.
+void group_rows(const void* ids, bool ids_are_64, int64_t count, int64_t key_start, int64_t key_rows,
+                const workspace_layout& l, char* ws, cudaStream_t stream, apply_params* p)
+{
+  auto* keys_in         = reinterpret_cast<uint32_t*>(ws + l.keys_in);
+  auto* keys_out        = reinterpret_cast<uint32_t*>(ws + l.keys_out);
+  auto* pos_in          = reinterpret_cast<int32_t*>(ws + l.pos_in);
+  auto* pos_out         = reinterpret_cast<int32_t*>(ws + l.pos_out);
+  auto* heads           = reinterpret_cast<int32_t*>(ws + l.heads);
+  auto* counters        = reinterpret_cast<int32_t*>(ws + l.counters);
+  const unsigned blocks = static_cast<unsigned>((count + kThreads - 1) / kThreads);
+  keys_kernel<<<blocks, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, count, key_start, key_rows, keys_in, pos_in);
+  size_t cub_bytes = l.cub_bytes;
+  WGB_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(ws + l.cub, cub_bytes, keys_in, keys_out, pos_in, pos_out,
+                                                 static_cast<int>(count), 0, key_bits(key_rows), stream));
+  WGB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 3 * sizeof(int32_t), stream));
+  size_t select_bytes = l.cub_bytes;
+  WGB_CUDA_CHECK(cub::DeviceSelect::If(ws + l.cub, select_bytes, thrust::counting_iterator<int>(0), heads, counters,
+                                       static_cast<int>(count), is_run_head{keys_out}, stream));
+  p->keys = keys_out, p->positions = pos_out, p->heads = heads, p->head_count = counters, p->n = count;
+  p->sentinel   = static_cast<uint32_t>(key_rows);
+  p->long_count = counters + 1, p->slot_count = counters + 2;
+  p->long_first = reinterpret_cast<int32_t*>(ws + l.long_first);
+  p->long_len   = reinterpret_cast<int32_t*>(ws + l.long_len);
+  p->long_slot  = reinterpret_cast<int32_t*>(ws + l.long_slot);
+  p->long_beta  = reinterpret_cast<float2*>(ws + l.long_beta);
+  p->long_run   = reinterpret_cast<int32_t*>(ws + l.long_run);
+  p->slot_run   = reinterpret_cast<int32_t*>(ws + l.slot_run);
+  p->slot_block = reinterpret_cast<int32_t*>(ws + l.slot_block);
+  p->partial    = reinterpret_cast<float*>(ws + l.partial);
+  p->unique_ids = nullptr, p->id_base = 0;
+}
+
+int apply_grid(int64_t count)
+{
+  static int sm_count = [] {
+    int dev = 0, n = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }();
+  // One CTA per tile of kTileRuns distinct rows, grid-stride; the number of rows is only known
+  // on the device, so the grid covers the case that every gradient row has its own id.
+  const int64_t tiles = (count + kTileRuns - 1) / kTileRuns;
+  return static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(sm_count) * 2 * 8));
+}
+
+struct owner_table {
+  int world;
+  int64_t first_row[kMaxOwnerRanks + 1];
+};
+
+// Runs are ascending by id, so every owner's runs are one contiguous range: thread r finds where
+// owner r's range starts (first run whose id is >= first_row[r]) by bisection over the heads.
+__global__ void owner_ranges_kernel(const uint32_t* keys, const int32_t* heads, const int32_t* head_count,
+                                    const owner_table t, int64_t* counts, int64_t* starts)
+{
+  __shared__ int64_t s_start[kMaxOwnerRanks + 1];
+  const int r = threadIdx.x;
+  if (r <= t.world) {
+    int lo = 0, hi = *head_count;  // the run of rejected ids (key = table rows), if any, stays right of every range
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (static_cast<int64_t>(keys[heads[mid]]) < t.first_row[r]) lo = mid + 1;
+      else hi = mid;
+    }
+    s_start[r] = lo;
+  }
+  __syncthreads();
+  if (r < t.world) {
+    starts[r] = s_start[r];
+    counts[r] = s_start[r + 1] - s_start[r];
+  }
+}
+
+}  // namespace
+
+size_t reduce_duplicates_workspace_bytes(int64_t count, int64_t table_rows, int64_t dim)
+{
+  return layout_for(count, table_rows, dim).total;
+}
+
+bool reduce_duplicates_supported(int64_t count, int64_t table_rows, int world)
+{
+  return count < (int64_t(1) << 31) && table_rows < (int64_t(1) << 32) - 1 && world <= kMaxOwnerRanks;
+}
+
+void reduce_duplicates(const void* ids, bool ids_are_64, int64_t count, const float* grads, int64_t grad_stride,
+                       int64_t dim, const int64_t* first_row, int world, void* workspace, int64_t* unique_ids,
+                       float* sums, int64_t* owner_counts, int64_t* owner_starts, cudaStream_t stream)
+{
+  WGB_EXPECTS(count > 0 && dim > 0, "nothing to reduce");
+  WGB_EXPECTS(reduce_duplicates_supported(count, first_row[world], world), "gradient list too large to pre-reduce");
+  const int64_t table_rows = first_row[world];
+  const workspace_layout l = layout_for(count, table_rows, dim);
+  apply_params p{};
+  group_rows(ids, ids_are_64, count, 0, table_rows, l, static_cast<char*>(workspace), stream, &p);
+  p.grads = grads, p.grad_stride = grad_stride, p.dim = static_cast<int>(dim);
+  p.weights = sums, p.weight_stride = dim;
+  p.state = nullptr, p.beta12t = nullptr;
+  p.h.type     = WHOLEGRAPH_OPT_NONE;
+  p.unique_ids = unique_ids, p.id_base = 0;
+  owner_table t;
+  t.world = world;
+  for (int r = 0; r <= world; r++) t.first_row[r] = first_row[r];
+  owner_ranges_kernel<<<1, kMaxOwnerRanks + 1, 0, stream>>>(p.keys, p.heads, p.head_count, t, owner_counts,
+                                                            owner_starts);
+  const bool vec4 = dim % 4 == 0 && grad_stride % 4 == 0 && reinterpret_cast<uintptr_t>(grads) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(sums) % 16 == 0;
+  launch_apply_opt<float>(p, vec4, apply_grid(count), stream);
+  count_kernel_launch(7);
+  WGB_LAUNCH_CHECK(stream);
+}
+
 void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stream)
 {
   if (a.count == 0 || a.dim == 0) return;
@@ -511,60 +741,26 @@ void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stre
   WGB_EXPECTS(a.weight_dtype == WHOLEGRAPH_DT_FLOAT || a.weight_dtype == WHOLEGRAPH_DT_HALF ||
                 a.weight_dtype == WHOLEGRAPH_DT_BF16,
               "only float, half and bf16 tables can be trained");
+  WGB_EXPECTS(a.hyper.type == WHOLEGRAPH_OPT_SGD || a.hyper.type == WHOLEGRAPH_OPT_LAZY_ADAM ||
+                a.hyper.type == WHOLEGRAPH_OPT_ADAGRAD || a.hyper.type == WHOLEGRAPH_OPT_RMSPROP,
+              "unknown optimizer type %d", (int)a.hyper.type);
   WGB_EXPECTS(a.hyper.type == WHOLEGRAPH_OPT_SGD || a.state != nullptr, "optimizer state is missing");
   WGB_EXPECTS(a.hyper.type != WHOLEGRAPH_OPT_LAZY_ADAM || a.beta12t != nullptr, "beta12t is missing");
   const workspace_layout l = layout_for(a.count, a.local_rows, a.dim);
-  char* ws                 = static_cast<char*>(workspace);
-  auto* keys_in            = reinterpret_cast<uint32_t*>(ws + l.keys_in);
-  auto* keys_out           = reinterpret_cast<uint32_t*>(ws + l.keys_out);
-  auto* pos_in             = reinterpret_cast<int32_t*>(ws + l.pos_in);
-  auto* pos_out            = reinterpret_cast<int32_t*>(ws + l.pos_out);
-  auto* heads              = reinterpret_cast<int32_t*>(ws + l.heads);
-  auto* counters           = reinterpret_cast<int32_t*>(ws + l.counters);
-  auto* head_count         = counters;
-  const unsigned blocks    = static_cast<unsigned>((a.count + kThreads - 1) / kThreads);
-
-  keys_kernel<<<blocks, kThreads, 0, stream>>>(a.ids, a.ids_are_64 ? 1 : 0, a.count, a.local_start, a.local_rows,
-                                               keys_in, pos_in);
-  size_t cub_bytes = l.cub_bytes;
-  WGB_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(ws + l.cub, cub_bytes, keys_in, keys_out, pos_in, pos_out,
-                                                 static_cast<int>(a.count), 0, key_bits(a.local_rows),
-                                                 stream));
-  WGB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 3 * sizeof(int32_t), stream));
-  size_t select_bytes = l.cub_bytes;
-  WGB_CUDA_CHECK(cub::DeviceSelect::If(ws + l.cub, select_bytes, thrust::counting_iterator<int>(0), heads,
-                                       head_count, static_cast<int>(a.count), is_run_head{keys_out}, stream));
-
-  apply_params p;
-  p.keys = keys_out, p.positions = pos_out, p.heads = heads, p.head_count = head_count, p.n = a.count;
-  p.sentinel = static_cast<uint32_t>(a.local_rows);
+  apply_params p{};
+  group_rows(a.ids, a.ids_are_64, a.count, a.local_start, a.local_rows, l, static_cast<char*>(workspace), stream, &p);
   p.grads = a.grads, p.grad_stride = a.grad_stride, p.dim = static_cast<int>(a.dim);
   p.weights = a.weights, p.weight_stride = a.weight_stride;
   p.state = a.state, p.state_stride = a.state_stride, p.v_offset = a.v_offset, p.beta12t = a.beta12t;
   p.h = a.hyper;
   p.weight_cache = a.weight_cache, p.state_cache = a.state_cache;
-  p.long_count = counters + 1, p.slot_count = counters + 2;
-  p.long_first = reinterpret_cast<int32_t*>(ws + l.long_first);
-  p.long_len   = reinterpret_cast<int32_t*>(ws + l.long_len);
-  p.long_slot  = reinterpret_cast<int32_t*>(ws + l.long_slot);
-  p.slot_run   = reinterpret_cast<int32_t*>(ws + l.slot_run);
-  p.slot_block = reinterpret_cast<int32_t*>(ws + l.slot_block);
-  p.partial    = reinterpret_cast<float*>(ws + l.partial);
   const size_t w_es = wholegraph_dtype_get_element_size(a.weight_dtype);
   const bool vec4   = a.dim % 4 == 0 && a.grad_stride % 4 == 0 &&
                     reinterpret_cast<uintptr_t>(a.grads) % 16 == 0 && a.weight_stride % 4 == 0 &&
                     reinterpret_cast<uintptr_t>(a.weights) % (4 * w_es) == 0 &&
                     (a.state == nullptr || (a.state_stride % 4 == 0 && a.v_offset % 4 == 0 &&
                                             reinterpret_cast<uintptr_t>(a.state) % 16 == 0));
-  static int sm_count = [] {
-    int dev = 0, n = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n;
-  }();
-  // One warp per distinct row, grid-stride; the number of rows is only known on the device.
-  const int64_t warps_wanted = a.count;
-  int ctas = static_cast<int>(std::min<int64_t>((warps_wanted + 7) / 8, static_cast<int64_t>(sm_count) * 8 * 4));
+  const int ctas = apply_grid(a.count);
   if (a.weight_dtype == WHOLEGRAPH_DT_FLOAT)
     launch_apply_opt<float>(p, vec4, ctas, stream);
   else if (a.weight_dtype == WHOLEGRAPH_DT_HALF)

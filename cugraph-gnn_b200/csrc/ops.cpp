@@ -51,7 +51,6 @@ void exchange_plan::build(const void* ids, bool ids_are_64, int64_t n,
   positions  = static_cast<int64_t*>(positions_buf.device(n, WHOLEGRAPH_DT_INT64));
   // Device layout: [send counts | send starts | recv counts], world entries each.
   int64_t* cdev = static_cast<int64_t*>(counts_dev.device(3 * world, WHOLEGRAPH_DT_INT64));
-  int64_t* cpin = static_cast<int64_t*>(counts_pin.pinned(3 * world, WHOLEGRAPH_DT_INT64));
   if (dedup) {
     void* ws = workspace.device_bytes(unique_workspace_bytes(n, first_row[world]));
     inverse  = positions;  // same storage, other meaning
@@ -63,6 +62,27 @@ void exchange_plan::build(const void* ids, bool ids_are_64, int64_t n,
     partition_by_owner(ids, ids_are_64, n, first_row.data(), world, ws, sorted_ids, positions, cdev,
                        cdev + world, stream);
   }
+  exchange_counts_and_ids(cdev, comm, stream);
+}
+
+void exchange_plan::build_grouped(int64_t* grouped_ids, int64_t* group_counts_dev, wholegraph_comm_* comm,
+                                  cudaStream_t stream)
+{
+  world = comm->world_size;
+  me    = comm->world_rank;
+  send_counts.assign(world, 0);
+  send_displs.assign(world, 0);
+  recv_counts.assign(world, 0);
+  recv_displs.assign(world, 0);
+  sorted_ids = grouped_ids;
+  positions  = nullptr;
+  exchange_counts_and_ids(group_counts_dev, comm, stream);
+  count = total_send;
+}
+
+void exchange_plan::exchange_counts_and_ids(int64_t* cdev, wholegraph_comm_* comm, cudaStream_t stream)
+{
+  int64_t* cpin = static_cast<int64_t*>(counts_pin.pinned(3 * world, WHOLEGRAPH_DT_INT64));
   comm->alltoall(cdev, cdev + 2 * world, sizeof(int64_t), stream);
   WGB_CUDA_CHECK(cudaMemcpyAsync(cpin, cdev, sizeof(int64_t) * 3 * world, cudaMemcpyDeviceToHost,
                                  stream));
@@ -90,11 +110,8 @@ struct phase_timer {
   std::vector<std::pair<const char*, cudaEvent_t>> marks;
   explicit phase_timer(cudaStream_t s) : stream(s)
   {
-    static const bool enabled = [] {
-      const char* e = getenv("WG_TIMING");
-      return e != nullptr && e[0] == '1';
-    }();
-    on = enabled;
+    const char* e = getenv("WG_TIMING");
+    on            = e != nullptr && e[0] == '1';
   }
   void mark(const char* name)
   {
@@ -124,11 +141,9 @@ struct phase_timer {
 static int exchange_chunk_count(size_t bytes_out)
 {
   // WG_EXCHANGE_CHUNKS overrides the number of pipeline chunks (tuning only).
-  static const int forced = [] {
-    const char* e = getenv("WG_EXCHANGE_CHUNKS");
-    return e != nullptr ? std::max(1, atoi(e)) : 0;
-  }();
-  if (forced > 0) return forced;
+  const char* e    = getenv("WG_EXCHANGE_CHUNKS");
+  const int forced = e != nullptr ? std::max(1, atoi(e)) : 0;
+  if (forced > 0) return std::min(forced, 16);
   return bytes_out < (size_t(16) << 20) ? 1 : 4;
 }
 
@@ -283,10 +298,8 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
   timer.mark("start");
   exchange_plan plan(env);
   // WG_GATHER_DEDUP=0 routes every request, duplicates included, as the reference does.
-  static const bool dedup_wanted = [] {
-    const char* e = getenv("WG_GATHER_DEDUP");
-    return e == nullptr || e[0] != '0';
-  }();
+  const char* dedup_env   = getenv("WG_GATHER_DEDUP");
+  const bool dedup_wanted = dedup_env == nullptr || dedup_env[0] != '0';
   const bool dedup = cache == nullptr && dedup_wanted && unique_supported(n, first_row[W]);
   plan.build(ids, ids_are_64, n, first_row, comm, stream, dedup);
   timer.mark(dedup ? "unique+counts+ids" : "partition+counts+ids");

@@ -29,6 +29,12 @@ struct exchange_plan {
   void build(const void* ids, bool ids_are_64, int64_t n, const std::vector<int64_t>& first_row,
              wholegraph_comm_* comm, cudaStream_t stream, bool dedup = false);
 
+  // Same exchange for a list that is already grouped by owner: `grouped_ids` holds the ids to
+  // route and `group_counts_dev` the device layout [counts | starts | scratch], `world` entries
+  // each, that describes its groups.  sorted_ids aliases grouped_ids; positions stays null.
+  void build_grouped(int64_t* grouped_ids, int64_t* group_counts_dev, wholegraph_comm_* comm,
+                     cudaStream_t stream);
+
   int world = 1, me = 0;
   int64_t count = 0;  // length of the request list
   // Host copies, in rows.  send_* describe this rank's requests grouped by owner (positions in
@@ -41,6 +47,7 @@ struct exchange_plan {
   int64_t* inverse    = nullptr;  // device, dedup only: slot in sorted_ids of every list position
 
  private:
+  void exchange_counts_and_ids(int64_t* cdev, wholegraph_comm_* comm, cudaStream_t stream);
   temp_buffer workspace, sorted_ids_buf, positions_buf, recv_ids_buf, counts_dev, counts_pin;
 };
 

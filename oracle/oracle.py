@@ -176,6 +176,19 @@ def dedup_gradients(indices: np.ndarray, grads: np.ndarray, grads_bf16: bool = F
     return uniq[:u].copy(), sums[:u].copy()
 
 
+def dedup_gradients_by_rank(rank_indices, rank_grads, block: int = 256):
+    """Two-level order of the distributed gradient apply when every rank pre-sums its own
+    duplicates: per rank, duplicates are added in arrival order (runs longer than `block` block by
+    block); the owner then adds the per-rank sums of an id in rank order.  Returns (unique ids,
+    fp32 sums) over all ranks."""
+    ids, sums = [], []
+    for idx, g in zip(rank_indices, rank_grads):
+        u, s = dedup_gradients(idx, g, block=block)
+        ids.append(u)
+        sums.append(s)
+    return dedup_gradients(np.concatenate(ids), np.concatenate(sums), block=block)
+
+
 def optimizer_apply(opt: int, ids: np.ndarray, grads: np.ndarray, weights: np.ndarray, *, lr: float,
                     state: np.ndarray | None = None, v_offset: int = 0, beta12t: np.ndarray | None = None,
                     local_start: int = 0, weight_decay: float = 0.0, epsilon: float = 1e-8,

@@ -129,7 +129,7 @@ def main():
         wgb.destroy_wholegraph_tensor(t)
 
     def check_gradient_apply(mem_type, opt_type, opt_code, rows, dim, n, steps, table_dtype=torch.float32,
-                             cache_type=None):
+                             cache_type=None, hot=0):
         print(f"rank {rank}: gradient apply {mem_type.name} opt={opt_code} rows={rows} dim={dim} "
               f"cache={cache_type}", flush=True)
         policy = None
@@ -159,6 +159,8 @@ def main():
                 rng = np.random.default_rng(1000 * step + r)
                 ids_r = rng.integers(0, rows, size=n).astype(np.int64)
                 ids_r[: n // 3] = ids_r[n // 3: 2 * (n // 3)]
+                if hot:                       # one id with more duplicates per rank than a summation block
+                    ids_r[rng.permutation(n)[:hot]] = rows // 2
                 all_ids.append(ids_r)
                 all_grads.append(rng.uniform(-1, 1, size=(n, dim)).astype(np.float32))
             d_ids, d_grads = torch.from_numpy(all_ids[rank]).cuda(), torch.from_numpy(all_grads[rank]).cuda()
@@ -168,8 +170,13 @@ def main():
             wgb.destroy_wholegraph_tensor(wi)
             wgb.destroy_wholegraph_tensor(wg)
             wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
-            # oracle: duplicates summed in rank-then-arrival order, every row updated once
-            uniq, sums = orc.dedup_gradients(np.concatenate(all_ids), np.concatenate(all_grads))
+            # oracle: every row updated once with the sum of its gradients - by default per-rank sums
+            # (arrival order) added in rank order, with WG_GRADIENT_PRESUM=0 one chain in
+            # rank-then-arrival order as in the reference (runs over 256 rows block by block)
+            if os.environ.get("WG_GRADIENT_PRESUM", "1") == "0":
+                uniq, sums = orc.dedup_gradients(np.concatenate(all_ids), np.concatenate(all_grads), block=256)
+            else:
+                uniq, sums = orc.dedup_gradients_by_rank(all_ids, all_grads)
             orc.optimizer_apply(opt_code, uniq, sums, w_host, lr=0.01, state=state, v_offset=padded, beta12t=beta,
                                 weight_decay=0.01, weights_bf16=(table_dtype == torch.bfloat16))
         if policy is not None:
@@ -217,6 +224,7 @@ def main():
         OT = wgb.WholeGraphOptimizerType
         check_gradient_apply(MT.MtDistributed, OT.OptLazyAdam, 2, 20_011, 64, 6_000, 3)
         check_gradient_apply(MT.MtContinuous, OT.OptSgd, 1, 5_000, 33, 3_000, 2)
+        check_gradient_apply(MT.MtDistributed, OT.OptLazyAdam, 2, 9_000, 32, 4_000, 2, hot=700)
         check_gradient_apply(MT.MtDistributed, OT.OptAdaGrad, 4, 8_000, 100, 3_000, 2, torch.float16)
         check_gradient_apply(MT.MtDistributed, OT.OptRmsProp, 3, 3_000, 256, 9_000, 2, torch.bfloat16)
         wgb.destroy_communicator(comm)

@@ -228,3 +228,29 @@ def test_round_robin_map_is_the_literal_reference_formula(orc):
     got = orc.round_robin_map(ids, rr=4, world=2, entry_start=100)
     want = 100 + 4 * ((ids // 4) // 2) + ids % 4
     assert np.array_equal(got, want)
+
+
+def test_two_level_gradient_sum_is_the_single_chain_up_to_rounding(orc):
+    """Per-rank sums added in rank order (the order of the distributed gradient apply) against the
+    single rank-then-arrival chain and against float64."""
+    rng = np.random.default_rng(11)
+    ranks, n, dim, rows = 4, 3000, 8, 500
+    ids = [rng.integers(0, rows, size=n) for _ in range(ranks)]
+    for r in range(ranks):
+        ids[r][:400] = 17                                   # longer than a block on every rank
+    grads = [rng.normal(0, 1, size=(n, dim)).astype(np.float32) for _ in range(ranks)]
+    u2, s2 = orc.dedup_gradients_by_rank(ids, grads, block=256)
+    u1, s1 = orc.dedup_gradients(np.concatenate(ids), np.concatenate(grads))
+    assert np.array_equal(u1, u2)
+    exact = np.zeros((rows, dim))
+    np.add.at(exact, np.concatenate(ids), np.concatenate(grads).astype(np.float64))
+    scale = np.zeros((rows, dim))
+    np.add.at(scale, np.concatenate(ids), np.abs(np.concatenate(grads)).astype(np.float64))
+    for s in (s1, s2):                                      # both orders are fp32 sums of the same terms
+        assert np.all(np.abs(s - exact[u1]) <= 1e-6 * scale[u1])
+    # ids that live on one rank only are summed identically by both orders
+    solo_ids = [np.arange(r * 50, r * 50 + 50).repeat(3) for r in range(ranks)]
+    solo_g = [rng.normal(0, 1, size=(150, dim)).astype(np.float32) for _ in range(ranks)]
+    ua, sa = orc.dedup_gradients_by_rank(solo_ids, solo_g)
+    ub, sb = orc.dedup_gradients(np.concatenate(solo_ids), np.concatenate(solo_g))
+    assert np.array_equal(ua, ub) and np.array_equal(sa, sb)
