@@ -196,6 +196,8 @@ void destroy_comm(wholegraph_comm_* comm)
   std::sort(left.begin(), left.end(),
             [](wholegraph_handle_* a, wholegraph_handle_* b) { return a->id < b->id; });
   for (auto* h : left) destroy_handle(h);
+  if (comm->barrier_word) cudaFree(comm->barrier_word);
+  if (comm->arena_idle) cudaEventDestroy(comm->arena_idle);
   if (comm->dev_stage) cudaFree(comm->dev_stage);
   if (comm->pin_stage) cudaFreeHost(comm->pin_stage);
   if (comm->side_stream) cudaStreamDestroy(comm->side_stream);
@@ -354,6 +356,26 @@ void wholegraph_comm_::sendrecv(const void* send, size_t send_bytes, int to, voi
   if (send_bytes > 0) WGB_NCCL_CHECK(wgb::nccl_lib().Send(send, send_bytes, ncclInt8, to, nc, stream));
   if (recv_bytes > 0) WGB_NCCL_CHECK(wgb::nccl_lib().Recv(recv, recv_bytes, ncclInt8, from, nc, stream));
   WGB_NCCL_CHECK(wgb::nccl_lib().GroupEnd());
+}
+
+void wholegraph_comm_::allgather(const void* send, void* recv, size_t bytes, cudaStream_t stream)
+{
+  if (world_size == 1) {
+    if (recv != send) WGB_CUDA_CHECK(cudaMemcpyAsync(recv, send, bytes, cudaMemcpyDeviceToDevice, stream));
+    return;
+  }
+  WGB_NCCL_CHECK(wgb::nccl_lib().AllGather(send, recv, bytes, ncclInt8, static_cast<ncclComm_t>(nccl), stream));
+}
+
+void wholegraph_comm_::stream_barrier(cudaStream_t stream)
+{
+  if (world_size == 1) return;
+  if (barrier_word == nullptr) {
+    WGB_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&barrier_word), 256));
+    WGB_CUDA_CHECK(cudaMemset(barrier_word, 0, 256));
+  }
+  WGB_NCCL_CHECK(wgb::nccl_lib().AllReduce(barrier_word, barrier_word + 32, 1, ncclInt32, ncclSum,
+                                       static_cast<ncclComm_t>(nccl), stream));
 }
 
 void wholegraph_comm_::alltoall(const void* send, void* recv, size_t bytes, cudaStream_t stream)

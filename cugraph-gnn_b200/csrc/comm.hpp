@@ -38,6 +38,16 @@ struct wholegraph_comm_ {
   std::vector<cudaEvent_t> events;
   cudaEvent_t event(size_t i);  // i-th pooled event (created on demand, timing disabled)
 
+  // Peer-mapped exchange arena: a CONTINUOUS/DEVICE allocation with one region of arena_bytes
+  // per rank, mapped on every rank, into which owners write the rows a rank asked for (and
+  // senders their gradient sums) with plain stores over NVLink.  Created on first use and grown
+  // collectively; null when peer mapping is not available (then every exchange goes through NCCL).
+  wholegraph_handle_* arena = nullptr;
+  size_t arena_bytes        = 0;
+  bool arena_unavailable    = false;
+  cudaEvent_t arena_idle    = nullptr;  // this rank's last read of its own region
+  int* barrier_word         = nullptr;  // device word of stream_barrier
+
   // ---- host collectives (blocking; caller memory is pageable host memory) ----
   void host_allgather(const void* send, void* recv, size_t bytes_per_rank);
   void host_alltoall(const void* send, void* recv, size_t bytes_per_pair);
@@ -64,6 +74,11 @@ struct wholegraph_comm_ {
                 int from, cudaStream_t stream);
   // Fixed-size alltoall of device buffers.
   void alltoall(const void* send, void* recv, size_t bytes_per_pair, cudaStream_t stream);
+  // Fixed-size allgather of device buffers.
+  void allgather(const void* send, void* recv, size_t bytes_per_rank, cudaStream_t stream);
+  // Barrier in stream order: work enqueued on `stream` after it starts only when every rank's
+  // work enqueued before it has finished (no host synchronisation).
+  void stream_barrier(cudaStream_t stream);
   // Poll the communicator for an asynchronous error; throws comm_error.
   void check_async_error();
 };

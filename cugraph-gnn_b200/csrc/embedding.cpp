@@ -400,6 +400,8 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   const size_t row_b    = static_cast<size_t>(e->dim) * sizeof(float);
   exchange_plan plan(env);
   temp_buffer send_buf(env), recv_buf(env), uid_buf(env), counts_buf(env), presum_ws(env);
+  // A call on another stream may still be reading this rank's arena region.
+  if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->arena_idle, 0));
   char* recv = nullptr;
 
   // WG_GRADIENT_PRESUM=0 routes every gradient row, as the reference does.  By default each rank
@@ -411,22 +413,39 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   if (presum) {
     int64_t* cdev = static_cast<int64_t*>(counts_buf.device(3 * W, WHOLEGRAPH_DT_INT64));
     int64_t* uids = static_cast<int64_t*>(uid_buf.device(std::max<int64_t>(n, 1), WHOLEGRAPH_DT_INT64));
-    char* sums    = static_cast<char*>(send_buf.device_bytes(std::max<size_t>(1, n * row_b)));
+    void* pws     = n > 0 ? presum_ws.device_bytes(reduce_duplicates_workspace_bytes(n, first_row[W], e->dim)) : nullptr;
     if (n > 0) {
-      reduce_duplicates(ids, ids_are_64, n, g, gd->strides[0], e->dim, first_row.data(), W,
-                        presum_ws.device_bytes(reduce_duplicates_workspace_bytes(n, first_row[W], e->dim)), uids,
-                        reinterpret_cast<float*>(sums), cdev, cdev + W, stream);
+      reduce_duplicates_group(ids, ids_are_64, n, e->dim, first_row.data(), W, pws, uids, cdev, cdev + W, stream);
     } else {
       WGB_CUDA_CHECK(cudaMemsetAsync(cdev, 0, sizeof(int64_t) * 2 * W, stream));
     }
     plan.build_grouped(uids, cdev, comm, stream);
-    recv = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
-    if (plan.send_counts[me] > 0)  // own rows go straight into their slot of the receive buffer
-      WGB_CUDA_CHECK(cudaMemcpyAsync(recv + plan.recv_displs[me] * row_b, sums + plan.send_displs[me] * row_b,
-                                     plan.send_counts[me] * row_b, cudaMemcpyDeviceToDevice, stream));
-    auto nothing = [](const list_segments&) {};  // rows are already where the exchange reads them
-    pipelined_exchange(comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, sums, recv,
-                       row_b, stream, nothing, nothing);
+    // With the peer-mapped arena the sums are written straight into their owner's region
+    // (summation and transfer in one kernel); otherwise into a dense buffer that NCCL moves.
+    const bool peer = ensure_peer_arena(comm, static_cast<size_t>(plan.max_total_recv()) * row_b, stream);
+    std::vector<float*> dest(W);
+    char* sums = nullptr;
+    if (peer) {
+      recv = peer_arena_region(comm, me);
+      for (int r = 0; r < W; r++)
+        dest[r] = reinterpret_cast<float*>(peer_arena_region(comm, r) + plan.arrival_start(me, r) * row_b);
+    } else {
+      sums = static_cast<char*>(send_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
+      recv = static_cast<char*>(recv_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
+      for (int r = 0; r < W; r++) dest[r] = reinterpret_cast<float*>(sums + plan.send_displs[r] * row_b);
+      // own rows go straight into their slot of the receive buffer
+      dest[me] = reinterpret_cast<float*>(recv + plan.recv_displs[me] * row_b);
+    }
+    if (n > 0)
+      reduce_duplicates_sum(n, first_row[W], g, gd->strides[0], e->dim, W, plan.send_counts.data(), dest.data(), pws,
+                            stream);
+    if (peer) {
+      comm->stream_barrier(stream);  // every sender's sums have landed
+    } else {
+      auto nothing = [](const list_segments&) {};  // rows are already where the exchange reads them
+      pipelined_exchange(comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, sums, recv,
+                         row_b, stream, nothing, nothing);
+    }
   } else {
     // Every gradient row goes to the owner of its id: the pipeline of a distributed scatter, with
     // fp32 rows on the wire.
@@ -454,11 +473,15 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
       },
       [](const list_segments&) {});  // the update below needs every row: nothing to do per chunk
   }
-  if (plan.total_recv == 0) return;
+  if (plan.total_recv == 0) {
+    if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));
+    return;
+  }
   a.ids = plan.recv_ids, a.ids_are_64 = true, a.count = plan.total_recv;
   a.grads = reinterpret_cast<const float*>(recv), a.grad_stride = e->dim;
   adjust(plan.recv_ids, true, plan.total_recv);
   sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(plan.total_recv, wl.rows, e->dim)), stream);
+  if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));
 }
 
 // Run `fn(mapped indices)`, remapping the ids first when the embedding is sharded round-robin.

@@ -129,8 +129,11 @@ struct apply_params {
   int32_t* long_slot;     // per long run: first partial-sum slot
   float2* long_beta;      // per long run: the row's stepped beta1^t, beta2^t (Lazy Adam)
   int32_t* long_run;      // per long run: its number among all runs (reduce-only mode)
-  int64_t* unique_ids;    // reduce-only mode: id of every run, ascending
-  int64_t id_base;        // reduce-only mode: id of key 0
+  // Reduce-only mode: runs [owner_first_run[o], owner_first_run[o + 1]) belong to owner o and the
+  // sums of run k go to owner_out[o] + (k - owner_first_run[o]) * dim floats (local or peer memory).
+  int owners;
+  int32_t owner_first_run[kMaxOwnerRanks + 1];
+  float* owner_out[kMaxOwnerRanks];
   int32_t* long_count;    // number of long runs
   int32_t* slot_count;    // number of partial-sum slots handed out
   int32_t* slot_run;      // per slot: long run it belongs to
@@ -201,6 +204,14 @@ __device__ __forceinline__ void load_grad(const float* g, bool on, float (&out)[
   } else {
     out[0] = __ldg(g);
   }
+}
+
+// Reduce-only mode: where the sums of run `run` go.
+__device__ __forceinline__ float* reduce_destination(const apply_params& p, int64_t run)
+{
+  int o = 0;
+  while (o + 1 < p.owners && run >= p.owner_first_run[o + 1]) o++;
+  return p.owner_out[o] + (run - p.owner_first_run[o]) * p.dim;
 }
 
 // Weights and state of columns [c, c + VEC) of one row, held in registers between the loads
@@ -280,7 +291,6 @@ __global__ void __launch_bounds__(kThreads, 2) apply_kernel(const apply_params p
     if (row == p.sentinel) pos0 = -1;  // ids this rank does not own sort last
     if (pos0 >= 0) {
       const int len = s_first[t + 1] - first;  // heads ascend: a run ends where the next one starts
-      if (OPT == WHOLEGRAPH_OPT_NONE) p.unique_ids[run] = p.id_base + row;
       float beta1t = 0.f, beta2t = 0.f;
       if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
         // per-row running beta1^t, beta2^t: multiplied on every touch of the row
@@ -324,9 +334,9 @@ __global__ void __launch_bounds__(kThreads, 2) apply_kernel(const apply_params p
       const uint32_t urow = s_row[r];
       const float beta1t  = OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? s_beta[r][0] : 0.f;
       const float beta2t  = OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? s_beta[r][1] : 0.f;
-      // reduce only: sums go to row <run number> of the output, which stands in for the table
-      const int64_t out_row = OPT == WHOLEGRAPH_OPT_NONE ? tile0 + r : static_cast<int64_t>(urow);
-      W* w_row     = weights + out_row * p.weight_stride;
+      // reduce only: the sums go to the run's row at its owner, which stands in for the table row
+      W* w_row = OPT == WHOLEGRAPH_OPT_NONE ? reinterpret_cast<W*>(reduce_destination(p, tile0 + r))
+                                            : weights + static_cast<int64_t>(urow) * p.weight_stride;
       float* s_rw  = p.state != nullptr ? p.state + static_cast<int64_t>(urow) * p.state_stride : nullptr;
       w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, urow, lane, reinterpret_cast<char*>(w_row)));
       if (s_rw != nullptr)
@@ -454,8 +464,8 @@ __global__ void __launch_bounds__(kThreads, 2) apply_long_kernel(const apply_par
     const int blocks   = (p.long_len[li] + kDedupBlock - 1) / kDedupBlock;
     const float* part  = p.partial + static_cast<int64_t>(p.long_slot[li]) * p.dim + c;
     const float2 beta  = p.long_beta[li];
-    const int64_t out_row = OPT == WHOLEGRAPH_OPT_NONE ? p.long_run[li] : static_cast<int64_t>(row);
-    W* w_row     = weights + out_row * p.weight_stride;
+    W* w_row = OPT == WHOLEGRAPH_OPT_NONE ? reinterpret_cast<W*>(reduce_destination(p, p.long_run[li]))
+                                          : weights + static_cast<int64_t>(row) * p.weight_stride;
     float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
     w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, row, lane, reinterpret_cast<char*>(w_row)));
     if (s_row != nullptr)
@@ -618,8 +628,28 @@ void round_robin_remap(const void* ids, void* out, bool ids_are_64, int64_t coun
 
 namespace {
 
-// Steps 1-3 of every pass: keys, stable sort, ordered run heads.  Fills the grouping fields of
-// `p` and its long-run scratch pointers.
+// The grouping fields of `p` and its long-run scratch pointers inside a workspace.
+void bind_workspace(int64_t count, int64_t key_rows, const workspace_layout& l, char* ws, apply_params* p)
+{
+  auto* counters = reinterpret_cast<int32_t*>(ws + l.counters);
+  p->keys        = reinterpret_cast<uint32_t*>(ws + l.keys_out);
+  p->positions   = reinterpret_cast<int32_t*>(ws + l.pos_out);
+  p->heads       = reinterpret_cast<int32_t*>(ws + l.heads);
+  p->head_count = counters, p->n = count;
+  p->sentinel   = static_cast<uint32_t>(key_rows);
+  p->long_count = counters + 1, p->slot_count = counters + 2;
+  p->long_first = reinterpret_cast<int32_t*>(ws + l.long_first);
+  p->long_len   = reinterpret_cast<int32_t*>(ws + l.long_len);
+  p->long_slot  = reinterpret_cast<int32_t*>(ws + l.long_slot);
+  p->long_beta  = reinterpret_cast<float2*>(ws + l.long_beta);
+  p->long_run   = reinterpret_cast<int32_t*>(ws + l.long_run);
+  p->slot_run   = reinterpret_cast<int32_t*>(ws + l.slot_run);
+  p->slot_block = reinterpret_cast<int32_t*>(ws + l.slot_block);
+  p->partial    = reinterpret_cast<float*>(ws + l.partial);
+  p->owners     = 0;
+}
+
+// Steps 1-3 of every pass: keys, stable sort, ordered run heads.
 void group_rows(const void* ids, bool ids_are_64, int64_t count, int64_t key_start, int64_t key_rows,
                 const workspace_layout& l, char* ws, cudaStream_t stream, apply_params* p)
 {
@@ -638,18 +668,7 @@ void group_rows(const void* ids, bool ids_are_64, int64_t count, int64_t key_sta
   size_t select_bytes = l.cub_bytes;
   WGB_CUDA_CHECK(cub::DeviceSelect::If(ws + l.cub, select_bytes, thrust::counting_iterator<int>(0), heads, counters,
                                        static_cast<int>(count), is_run_head{keys_out}, stream));
-  p->keys = keys_out, p->positions = pos_out, p->heads = heads, p->head_count = counters, p->n = count;
-  p->sentinel   = static_cast<uint32_t>(key_rows);
-  p->long_count = counters + 1, p->slot_count = counters + 2;
-  p->long_first = reinterpret_cast<int32_t*>(ws + l.long_first);
-  p->long_len   = reinterpret_cast<int32_t*>(ws + l.long_len);
-  p->long_slot  = reinterpret_cast<int32_t*>(ws + l.long_slot);
-  p->long_beta  = reinterpret_cast<float2*>(ws + l.long_beta);
-  p->long_run   = reinterpret_cast<int32_t*>(ws + l.long_run);
-  p->slot_run   = reinterpret_cast<int32_t*>(ws + l.slot_run);
-  p->slot_block = reinterpret_cast<int32_t*>(ws + l.slot_block);
-  p->partial    = reinterpret_cast<float*>(ws + l.partial);
-  p->unique_ids = nullptr, p->id_base = 0;
+  bind_workspace(count, key_rows, l, ws, p);
 }
 
 int apply_grid(int64_t count)
@@ -694,6 +713,16 @@ __global__ void owner_ranges_kernel(const uint32_t* keys, const int32_t* heads, 
   }
 }
 
+// Id of every run (ascending); the run of rejected ids is left out.
+__global__ void run_ids_kernel(const uint32_t* keys, const int32_t* heads, const int32_t* head_count,
+                               uint32_t sentinel, int64_t* unique_ids)
+{
+  const int64_t run = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (run >= *head_count) return;
+  const uint32_t key = keys[heads[run]];
+  if (key != sentinel) unique_ids[run] = key;
+}
+
 }  // namespace
 
 size_t reduce_duplicates_workspace_bytes(int64_t count, int64_t table_rows, int64_t dim)
@@ -706,9 +735,9 @@ bool reduce_duplicates_supported(int64_t count, int64_t table_rows, int world)
   return count < (int64_t(1) << 31) && table_rows < (int64_t(1) << 32) - 1 && world <= kMaxOwnerRanks;
 }
 
-void reduce_duplicates(const void* ids, bool ids_are_64, int64_t count, const float* grads, int64_t grad_stride,
-                       int64_t dim, const int64_t* first_row, int world, void* workspace, int64_t* unique_ids,
-                       float* sums, int64_t* owner_counts, int64_t* owner_starts, cudaStream_t stream)
+void reduce_duplicates_group(const void* ids, bool ids_are_64, int64_t count, int64_t dim, const int64_t* first_row,
+                             int world, void* workspace, int64_t* unique_ids, int64_t* owner_counts,
+                             int64_t* owner_starts, cudaStream_t stream)
 {
   WGB_EXPECTS(count > 0 && dim > 0, "nothing to reduce");
   WGB_EXPECTS(reduce_duplicates_supported(count, first_row[world], world), "gradient list too large to pre-reduce");
@@ -716,20 +745,40 @@ void reduce_duplicates(const void* ids, bool ids_are_64, int64_t count, const fl
   const workspace_layout l = layout_for(count, table_rows, dim);
   apply_params p{};
   group_rows(ids, ids_are_64, count, 0, table_rows, l, static_cast<char*>(workspace), stream, &p);
-  p.grads = grads, p.grad_stride = grad_stride, p.dim = static_cast<int>(dim);
-  p.weights = sums, p.weight_stride = dim;
-  p.state = nullptr, p.beta12t = nullptr;
-  p.h.type     = WHOLEGRAPH_OPT_NONE;
-  p.unique_ids = unique_ids, p.id_base = 0;
   owner_table t;
   t.world = world;
   for (int r = 0; r <= world; r++) t.first_row[r] = first_row[r];
   owner_ranges_kernel<<<1, kMaxOwnerRanks + 1, 0, stream>>>(p.keys, p.heads, p.head_count, t, owner_counts,
                                                             owner_starts);
-  const bool vec4 = dim % 4 == 0 && grad_stride % 4 == 0 && reinterpret_cast<uintptr_t>(grads) % 16 == 0 &&
-                    reinterpret_cast<uintptr_t>(sums) % 16 == 0;
+  run_ids_kernel<<<static_cast<unsigned>((count + kThreads - 1) / kThreads), kThreads, 0, stream>>>(
+    p.keys, p.heads, p.head_count, p.sentinel, unique_ids);
+  count_kernel_launch(6);
+  WGB_LAUNCH_CHECK(stream);
+}
+
+void reduce_duplicates_sum(int64_t count, int64_t table_rows, const float* grads, int64_t grad_stride, int64_t dim,
+                           int world, const int64_t* owner_counts, float* const* owner_out, void* workspace,
+                           cudaStream_t stream)
+{
+  const workspace_layout l = layout_for(count, table_rows, dim);
+  apply_params p{};
+  bind_workspace(count, table_rows, l, static_cast<char*>(workspace), &p);
+  p.grads = grads, p.grad_stride = grad_stride, p.dim = static_cast<int>(dim);
+  p.weights = nullptr, p.weight_stride = dim;
+  p.state = nullptr, p.beta12t = nullptr;
+  p.h.type = WHOLEGRAPH_OPT_NONE;
+  p.owners = world;
+  bool vec4 = dim % 4 == 0 && grad_stride % 4 == 0 && reinterpret_cast<uintptr_t>(grads) % 16 == 0;
+  int64_t first = 0;
+  for (int r = 0; r < world; r++) {
+    p.owner_first_run[r] = static_cast<int32_t>(first);
+    p.owner_out[r]       = owner_out[r];
+    first += owner_counts[r];
+    vec4 = vec4 && reinterpret_cast<uintptr_t>(owner_out[r]) % 16 == 0;
+  }
+  p.owner_first_run[world] = static_cast<int32_t>(first);
   launch_apply_opt<float>(p, vec4, apply_grid(count), stream);
-  count_kernel_launch(7);
+  count_kernel_launch(3);
   WGB_LAUNCH_CHECK(stream);
 }
 

@@ -70,19 +70,27 @@ size_t sparse_apply_workspace_bytes(int64_t count, int64_t local_rows, int64_t d
 void sparse_apply(const sparse_apply_args& a, void* workspace, cudaStream_t stream);
 
 // Sender-side half of a two-level reduction: group the gradient rows of one rank by id and write
-// one fp32 row of sums per distinct id, ascending by id (so that every owner's rows are one
-// contiguous range).  The order of additions inside a group is that of sparse_apply (arrival
-// order; groups longer than WHOLEGRAPH_B200_DEDUP_BLOCK rows block by block).
-//   unique_ids   [count]        distinct ids that some rank owns (0 <= id < first_row[world])
-//   sums         [count, dim]   dense rows of sums
-//   owner_counts / owner_starts  device arrays of `world` entries: rows for every owner and where
-//                                they start in unique_ids / sums
-// first_row is a HOST array of world + 1 entries.
+// one fp32 row of sums per distinct id.  Distinct ids ascend, so the rows of every owner are one
+// contiguous range of them.  The order of additions inside a group is that of sparse_apply
+// (arrival order; groups longer than WHOLEGRAPH_B200_DEDUP_BLOCK rows block by block).
+//
+// Step 1, reduce_duplicates_group: sort and group.
+//   unique_ids   [count]  distinct ids that some rank owns (0 <= id < first_row[world]), ascending
+//   owner_counts / owner_starts  device arrays of `world` entries: distinct ids per owner and
+//                                where they start in unique_ids
+//   first_row is a HOST array of world + 1 entries.
+// Step 2, reduce_duplicates_sum, once the caller knows owner_counts on the host: the sums of the
+// k-th distinct id of owner r are written to owner_out[r] + k * dim floats - local memory or a
+// peer's, so that summation and transfer are one kernel.  Same workspace, count, table rows
+// (= first_row[world]) and dim as in step 1, nothing else in between on that workspace.
 size_t reduce_duplicates_workspace_bytes(int64_t count, int64_t table_rows, int64_t dim);
 bool reduce_duplicates_supported(int64_t count, int64_t table_rows, int world);
-void reduce_duplicates(const void* ids, bool ids_are_64, int64_t count, const float* grads, int64_t grad_stride,
-                       int64_t dim, const int64_t* first_row, int world, void* workspace, int64_t* unique_ids,
-                       float* sums, int64_t* owner_counts, int64_t* owner_starts, cudaStream_t stream);
+void reduce_duplicates_group(const void* ids, bool ids_are_64, int64_t count, int64_t dim, const int64_t* first_row,
+                             int world, void* workspace, int64_t* unique_ids, int64_t* owner_counts,
+                             int64_t* owner_starts, cudaStream_t stream);
+void reduce_duplicates_sum(int64_t count, int64_t table_rows, const float* grads, int64_t grad_stride, int64_t dim,
+                           int world, const int64_t* owner_counts, float* const* owner_out, void* workspace,
+                           cudaStream_t stream);
 
 // Fill `count` floats with `value` (state initialisation).
 void fill_float(float* data, float value, int64_t count, cudaStream_t stream);

@@ -31,7 +31,7 @@ namespace wgb {
 
 exchange_plan::exchange_plan(wholegraph_env_func_t* env)
   : workspace(env), sorted_ids_buf(env), positions_buf(env), recv_ids_buf(env), counts_dev(env),
-    counts_pin(env)
+    counts_pin(env), matrix_dev(env)
 {
 }
 
@@ -82,17 +82,19 @@ void exchange_plan::build_grouped(int64_t* grouped_ids, int64_t* group_counts_de
 
 void exchange_plan::exchange_counts_and_ids(int64_t* cdev, wholegraph_comm_* comm, cudaStream_t stream)
 {
-  int64_t* cpin = static_cast<int64_t*>(counts_pin.pinned(3 * world, WHOLEGRAPH_DT_INT64));
-  comm->alltoall(cdev, cdev + 2 * world, sizeof(int64_t), stream);
-  WGB_CUDA_CHECK(cudaMemcpyAsync(cpin, cdev, sizeof(int64_t) * 3 * world, cudaMemcpyDeviceToHost,
-                                 stream));
+  // Every rank learns every rank's per-owner counts (world * world numbers) in one allgather.
+  int64_t* mdev = static_cast<int64_t*>(matrix_dev.device(static_cast<size_t>(world) * world, WHOLEGRAPH_DT_INT64));
+  int64_t* mpin = static_cast<int64_t*>(counts_pin.pinned(static_cast<size_t>(world) * world, WHOLEGRAPH_DT_INT64));
+  comm->allgather(cdev, mdev, sizeof(int64_t) * world, stream);
+  WGB_CUDA_CHECK(cudaMemcpyAsync(mpin, mdev, sizeof(int64_t) * world * world, cudaMemcpyDeviceToHost, stream));
   WGB_CUDA_CHECK(cudaStreamSynchronize(stream));  // the one host sync of a distributed op
   comm->check_async_error();
+  rows.assign(mpin, mpin + static_cast<size_t>(world) * world);
   total_send = total_recv = 0;
   for (int r = 0; r < world; r++) {
-    send_counts[r] = cpin[r];
-    send_displs[r] = cpin[world + r];
-    recv_counts[r] = cpin[2 * world + r];
+    send_counts[r] = rows[static_cast<size_t>(me) * world + r];
+    send_displs[r] = total_send;
+    recv_counts[r] = rows[static_cast<size_t>(r) * world + me];
     recv_displs[r] = total_recv;
     total_send += send_counts[r];
     total_recv += recv_counts[r];
@@ -100,6 +102,81 @@ void exchange_plan::exchange_counts_and_ids(int64_t* cdev, wholegraph_comm_* com
   recv_ids = static_cast<int64_t*>(recv_ids_buf.device(total_recv, WHOLEGRAPH_DT_INT64));
   comm->alltoallv(sorted_ids, send_counts.data(), send_displs.data(), recv_ids, recv_counts.data(),
                   recv_displs.data(), sizeof(int64_t), stream);
+}
+
+int64_t exchange_plan::group_start(int q, int r) const
+{
+  int64_t s = 0;
+  for (int k = 0; k < r; k++) s += rows[static_cast<size_t>(q) * world + k];
+  return s;
+}
+
+int64_t exchange_plan::arrival_start(int q, int r) const
+{
+  int64_t s = 0;
+  for (int k = 0; k < q; k++) s += rows[static_cast<size_t>(k) * world + r];
+  return s;
+}
+
+int64_t exchange_plan::max_total_send() const
+{
+  int64_t best = 0;
+  for (int q = 0; q < world; q++) best = std::max(best, group_start(q, world));
+  return best;
+}
+
+int64_t exchange_plan::max_total_recv() const
+{
+  int64_t best = 0;
+  for (int r = 0; r < world; r++) best = std::max(best, arrival_start(world, r));
+  return best;
+}
+
+bool ensure_peer_arena(wholegraph_comm_* comm, size_t bytes_per_rank, cudaStream_t stream)
+{
+  const char* e = getenv("WG_PEER_EXCHANGE");
+  if (comm->world_size == 1 || comm->arena_unavailable || (e != nullptr && e[0] == '0')) return false;
+  if (comm->arena_idle == nullptr)
+    WGB_CUDA_CHECK(cudaEventCreateWithFlags(&comm->arena_idle, cudaEventDisableTiming));
+  if (comm->arena != nullptr && comm->arena_bytes >= bytes_per_rank) return true;
+  // (Re)create, with head room.  Every rank takes this branch together: the size is the same
+  // everywhere and so is the current arena.  No peer touches the old regions any more: each
+  // rank has passed the stream barrier that ended the last exchange through them.
+  constexpr size_t kUnit = size_t(64) << 20;
+  const size_t want      = (std::max(bytes_per_rank + bytes_per_rank / 4, size_t(256) << 20) + kUnit - 1) / kUnit * kUnit;
+  WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
+  int ok = 1;
+  try {
+    if (comm->arena != nullptr) {
+      destroy_handle(comm->arena);
+      comm->arena = nullptr, comm->arena_bytes = 0;
+    }
+    comm->arena = create_handle(want * comm->world_size, comm, WHOLEGRAPH_MT_CONTINUOUS, WHOLEGRAPH_ML_DEVICE, want,
+                                nullptr);
+    comm->arena_bytes = want;
+  } catch (const std::exception& ex) {
+    WGB_WARN("no peer-mapped exchange arena (%s): distributed ops keep to NCCL", ex.what());
+    ok = 0;
+  }
+  std::vector<int> all(comm->world_size, 0);
+  comm->host_allgather(&ok, all.data(), sizeof(int));
+  for (int v : all) ok &= v;
+  if (!ok) {
+    if (comm->arena != nullptr) {
+      try {
+        destroy_handle(comm->arena);
+      } catch (...) {
+      }
+    }
+    comm->arena = nullptr, comm->arena_bytes = 0, comm->arena_unavailable = true;
+    return false;
+  }
+  return true;
+}
+
+char* peer_arena_region(wholegraph_comm_* comm, int rank)
+{
+  return static_cast<char*>(comm->arena->global_base) + comm->arena->part_offsets[rank];
 }
 
 // WG_TIMING=1: distributed gathers record CUDA events at their phase boundaries and print the
@@ -294,6 +371,8 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
     return;
   }
 
+  // A call on another stream may still be reading this rank's arena region.
+  if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->arena_idle, 0));
   phase_timer timer(stream);
   timer.mark("start");
   exchange_plan plan(env);
@@ -307,9 +386,13 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
   if (dedup) {
     // Distinct ids only: owners serve each row once into `rows` (own rows are gathered into
     // their slots locally), then one local gather expands them into the output.
+    // Where the arena is available the owners write the rows straight into the requester's
+    // region over NVLink (gather, cast and transfer in one kernel per requester); otherwise they
+    // pack them and NCCL moves them.
+    const bool peer = ensure_peer_arena(comm, static_cast<size_t>(plan.max_total_send()) * row_b, stream);
     temp_buffer serve_buf(env), rows_buf(env);
-    char* serve = static_cast<char*>(serve_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
-    char* rows  = static_cast<char*>(rows_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
+    char* rows = peer ? peer_arena_region(comm, me)
+                      : static_cast<char*>(rows_buf.device_bytes(std::max<size_t>(1, plan.total_send * row_b)));
     row_copy_args from_shard = g;  // local shard -> dense rows, by index, cast at the owner
     from_shard.dst_stride = dim, from_shard.dst_offset = 0, from_shard.dst_select = ROW_SEQUENTIAL;
     if (plan.send_counts[me] > 0) {
@@ -320,15 +403,31 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
       launch_row_copy(a, stream);
     }
     timer.mark("own_rows");
-    pipelined_exchange(
-      comm, plan.recv_counts, plan.recv_displs, plan.send_counts, plan.send_displs, serve, rows, row_b, stream,
-      [&](const list_segments& seg) {
+    if (peer) {
+      // No requester still reads its region from an earlier call: it joined this call's counts
+      // exchange, which this stream has passed, only after that read.
+      for (int step = 1; step < W; step++) {
+        const int q = (me + step) % W;
+        if (plan.recv_counts[q] == 0) continue;
         row_copy_args a = from_shard;
-        a.dst = serve, a.indices = plan.recv_ids;
-        a.segments = seg, a.count = seg.total();
+        a.dst     = peer_arena_region(comm, q) + plan.group_start(q, me) * row_b;
+        a.indices = plan.recv_ids + plan.recv_displs[q];
+        a.count   = plan.recv_counts[q];
         launch_row_copy(a, stream);
-      },
-      [](const list_segments&) {});
+      }
+      comm->stream_barrier(stream);  // every owner's rows have landed
+    } else {
+      char* serve = static_cast<char*>(serve_buf.device_bytes(std::max<size_t>(1, plan.total_recv * row_b)));
+      pipelined_exchange(
+        comm, plan.recv_counts, plan.recv_displs, plan.send_counts, plan.send_displs, serve, rows, row_b, stream,
+        [&](const list_segments& seg) {
+          row_copy_args a = from_shard;
+          a.dst = serve, a.indices = plan.recv_ids;
+          a.segments = seg, a.count = seg.total();
+          launch_row_copy(a, stream);
+        },
+        [](const list_segments&) {});
+    }
     timer.mark("exchange");
     row_copy_args expand;  // rows[inverse[i]] -> output row i; ids nobody owns leave their row untouched
     expand.src = rows, expand.src_dt = od.dtype, expand.src_stride = dim, expand.src_select = ROW_BY_INDEX;
@@ -336,6 +435,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
     expand.dst_select = ROW_SEQUENTIAL, expand.dim = dim, expand.sm_hint = sms;
     expand.indices = plan.inverse, expand.indices_are_64 = true, expand.count = n;
     launch_row_copy(expand, stream);
+    if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));
     timer.mark("expand");
     return;
   }

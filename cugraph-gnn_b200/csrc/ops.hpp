@@ -41,6 +41,14 @@ struct exchange_plan {
   // sorted_ids / positions); recv_* describe the requests other ranks sent here (in recv_ids).
   std::vector<int64_t> send_counts, send_displs, recv_counts, recv_displs;
   int64_t total_send = 0, total_recv = 0;
+  // rows[q * world + r]: rows rank q routes to rank r, known to every rank.  Groups sit in owner
+  // order, so rank q's group for owner r starts at group_start(q, r) in q's own numbering, and
+  // the rows rank q sends to owner r arrive at arrival_start(q, r) in r's receive numbering.
+  std::vector<int64_t> rows;
+  int64_t group_start(int q, int r) const;
+  int64_t arrival_start(int q, int r) const;
+  int64_t max_total_send() const;
+  int64_t max_total_recv() const;
   int64_t* sorted_ids = nullptr;  // device, global row ids grouped by owner
   int64_t* positions  = nullptr;  // device, list position of each sorted id
   int64_t* recv_ids   = nullptr;  // device, global row ids this rank must serve
@@ -48,7 +56,7 @@ struct exchange_plan {
 
  private:
   void exchange_counts_and_ids(int64_t* cdev, wholegraph_comm_* comm, cudaStream_t stream);
-  temp_buffer workspace, sorted_ids_buf, positions_buf, recv_ids_buf, counts_dev, counts_pin;
+  temp_buffer workspace, sorted_ids_buf, positions_buf, recv_ids_buf, counts_dev, counts_pin, matrix_dev;
 };
 
 // Row exchange of a distributed op, cut into chunks so that packing chunk k + 1, moving chunk k
@@ -78,6 +86,13 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
                         bool ids_are_64, int64_t n, void* out, const wholegraph_matrix_description_t& od,
                         wholegraph_env_func_t* env, cudaStream_t stream, int sms,
                         const cache_view* cache = nullptr, bool adjust_cache = false);
+
+// Peer-mapped exchange arena of a communicator with at least `bytes_per_rank` per rank.
+// Collective: every rank must pass the same size.  Returns false (on every rank alike) when peer
+// mapping is not available or WG_PEER_EXCHANGE=0; the caller then exchanges through NCCL.
+bool ensure_peer_arena(wholegraph_comm_* comm, size_t bytes_per_rank, cudaStream_t stream);
+// Region of `rank` as mapped into this process.
+char* peer_arena_region(wholegraph_comm_* comm, int rank);
 
 // First row of every rank's shard (world + 1 entries) for rows of `entry_bytes` bytes.
 std::vector<int64_t> entry_offsets_of(wholegraph_handle_* h, size_t entry_bytes);
