@@ -458,9 +458,15 @@ def main():
     else:
         peak, how = measured_hbm_peak()
         achieved = algorithmic / (ms_step * 1e-3) / 1e9
+        # DRAM bytes per launch from the ncu capture of this kernel on a 2 M-row table with the full
+        # 1,048,576-id list (profiles/row_copy_gather_c2.md): 520.4 MB read + 228.4 MB written; it
+        # grows with the ids processed, so it is scaled by them.
+        traffic = 748.8e6 * n_ids / 1_048_576 if workload == "c2" and out_dtype == torch.float16 else None
         roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                    "frac": achieved / peak, "traffic": None, "peak_source": how,
-                    "algorithmic_bytes_per_launch": algorithmic}
+                    "frac": achieved / peak, "traffic": traffic, "peak_source": how,
+                    "algorithmic_bytes_per_launch": algorithmic,
+                    "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, small-table "
+                                      "capture scaled by ids" if traffic else None}
 
     # ---- CPU oracle beside it (rank 0, N = 1 only) ----------------------------------------
     cpu = None

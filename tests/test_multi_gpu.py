@@ -19,7 +19,7 @@ def _device_count():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.parametrize("scenario", ["continuous", "distributed", "distributed-keepdups", "chunked", "optimizer", "optimizer-nopresum", "cache"])
+@pytest.mark.parametrize("scenario", ["continuous", "distributed", "distributed-keepdups", "chunked", "optimizer", "optimizer-nopresum", "optimizer-peerpush", "cache"])
 def test_multi_gpu_gather_scatter(scenario):
     world = min(_device_count(), int(os.environ.get("WG_TEST_WORLD", "8")))
     if world < 2:
@@ -31,6 +31,9 @@ def test_multi_gpu_gather_scatter(scenario):
             scenario = scenario.split("-")[0]
         if scenario.endswith("-nopresum"):       # every gradient row routed, one summation chain per id
             env["WG_GRADIENT_PRESUM"] = "0"
+            scenario = scenario.split("-")[0]
+        if scenario.endswith("-peerpush"):       # gradient sums written straight into the owner's arena region
+            env["WG_PEER_GRADIENT"] = "1"
             scenario = scenario.split("-")[0]
         logs = [open(os.path.join(rdv, f"rank{r}.log"), "w+") for r in range(world)]
         procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "mg_worker.py"), str(r), str(world), rdv, scenario],
