@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "c2", "c3", "c4", "c5", "cache"])
     ap.add_argument("--rows", type=int, default=0, help="override the table rows (profiling on a small case)")
     ap.add_argument("--ids", type=int, default=0, help="override the ids per rank")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -274,6 +274,81 @@ def run_sparse_adam(args, torch, dist, wgb, tu, comm, world, rank, local_rank):
         dist.destroy_process_group()
 
 
+def run_cached_gather(args, torch, wgb, tu, comm):
+    """Cached embedding gather on one GPU: a 10 M x 128 fp32 table behind a set-associative cache
+    holding one row in eight (sets of 32 lines over 256 rows), 1,048,576 Zipf(1.1) ids per step
+    over a seeded permutation, fp32 output.  Timed twice: lookups only (adjust_cache = False, after
+    the cache has been warmed) and with the LFU update of every step inside the timed region."""
+    import ctypes as C
+    dim = ROW_DIM
+    rows = args.rows or 10_000_000
+    n = args.ids or IDS_PER_RANK
+    DT, MT, ML, AT = (wgb.WholeGraphDataType, wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation,
+                      wgb.WholeGraphAccessType)
+    env = wgb.cached_env_fns()
+    policy = wgb.create_cache_policy(comm, MT.MtContinuous, ML.MlDevice, AT.AtReadWrite, 0.125)
+    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT.DtFloat), comm, MT.MtContinuous, ML.MlDevice,
+                               cache_policy=policy)
+    table = wgb.embedding_tensor(emb)
+    local_rows = C.c_size_t()
+    wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_count(C.byref(local_rows), table), "entry_count")
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    for s in range(0, local_rows.value, 2_000_000):
+        piece = torch.empty((min(2_000_000, local_rows.value - s), dim), dtype=torch.float32, device="cuda")
+        piece.uniform_(-1, 1, generator=gen)
+        tu.write_local_shard(table, piece, s)
+    perm = torch.randperm(rows, generator=torch.Generator(device="cuda").manual_seed(7), device="cuda")
+    batches = [zipf_ids(torch, n, rows, 1.1, perm, torch.Generator(device="cuda").manual_seed(100 + b))
+               for b in range(INDEX_BATCHES)]
+    del perm
+    wraps = [tu.wrap_torch_tensor(b) for b in batches]
+    out = torch.empty((n, dim), dtype=torch.float32, device="cuda")
+    wout = tu.wrap_torch_tensor(out)
+    stream = tu.current_stream_int()
+
+    def timed(adjust):
+        for i in range(args.warmup):
+            wgb.EmbeddingGatherForward(emb, wraps[i % INDEX_BATCHES], wout, adjust, env, stream)
+        torch.cuda.synchronize()
+        l0 = wgb.lib().wholegraph_b200_kernel_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            wgb.EmbeddingGatherForward(emb, wraps[i % INDEX_BATCHES], wout, adjust, env, stream)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps, wgb.lib().wholegraph_b200_kernel_launch_count() - l0
+
+    for i in range(2 * INDEX_BATCHES):      # warm the cache with every batch
+        wgb.EmbeddingGatherForward(emb, wraps[i % INDEX_BATCHES], wout, True, env, stream)
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms_lookup, launches = timed(False)
+    ms_adjust, _ = timed(True)
+    clocks = sampler.stop()
+    tags = wgb.embedding_cache_tensors(emb)[0]
+    sets = wgb.lib().wholegraph_tensor_get_tensor_description(tags).contents.sizes[0]
+    peak, how = measured_hbm_peak()
+    algorithmic = n * (2 * dim * 4 + 8 + 64)       # row read + row write + id + one 64-byte tag set per id
+    achieved = algorithmic / (ms_lookup * 1e-3) / 1e9
+    line = {"metric": "gathered embedding GB/s", "value": n * dim * 4 / (ms_lookup * 1e-3) / 1e9, "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_lookup,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"cached gather: {rows} x {dim} fp32 CONTINUOUS/DEVICE table behind a cache of ratio 1/8 "
+                                   f"({sets} sets of 32 lines), {n} int64 Zipf(1.1) ids per step, fp32 output, lookups only",
+                       "ms_per_step_with_lfu_update": ms_adjust,
+                       "value_with_lfu_update": n * dim * 4 / (ms_adjust * 1e-3) / 1e9},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": how, "algorithmic_bytes_per_launch": algorithmic}}
+    print(json.dumps(line), flush=True)
+    for w in wraps:
+        wgb.destroy_wholegraph_tensor(w)
+    wgb.destroy_wholegraph_tensor(wout)
+    wgb.destroy_embedding(emb)
+    wgb.destroy_cache_policy(policy)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -315,6 +390,11 @@ def main():
 
     if workload == "c5":
         run_sparse_adam(args, torch, dist, wgb, tu, comm, world, rank, local_rank)
+        return
+    if workload == "cache":
+        if multi:
+            raise SystemExit("the cache workload runs on one GPU")
+        run_cached_gather(args, torch, wgb, tu, comm)
         return
     MT = wgb.WholeGraphMemoryType
     mem_type, zipf_alpha, zipf_shift = MT.MtContinuous, None, 0.0

@@ -448,7 +448,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     } else {
       auto nothing = [](const list_segments&) {};  // rows are already where the exchange reads them
       pipelined_exchange(comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, sums, recv,
-                         row_b, stream, nothing, nothing);
+                         row_b, stream, nothing, nothing, 1);
     }
   } else {
     // Every gradient row goes to the owner of its id: the pipeline of a distributed scatter, with

@@ -215,12 +215,13 @@ struct phase_timer {
   }
 };
 
-static int exchange_chunk_count(size_t bytes_out)
+static int exchange_chunk_count(size_t bytes_out, int wanted)
 {
   // WG_EXCHANGE_CHUNKS overrides the number of pipeline chunks (tuning only).
   const char* e    = getenv("WG_EXCHANGE_CHUNKS");
   const int forced = e != nullptr ? std::max(1, atoi(e)) : 0;
   if (forced > 0) return std::min(forced, 16);
+  if (wanted > 0) return std::min(wanted, 16);
   return bytes_out < (size_t(16) << 20) ? 1 : 4;
 }
 
@@ -229,13 +230,13 @@ void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_
                         const std::vector<int64_t>& in_displs, char* out_buf, char* in_buf,
                         size_t row_bytes, cudaStream_t stream,
                         const std::function<void(const list_segments&)>& pack,
-                        const std::function<void(const list_segments&)>& unpack)
+                        const std::function<void(const list_segments&)>& unpack, int chunks)
 {
   const int W = comm->world_size, me = comm->world_rank;
   int64_t total_out = 0;
   for (int p = 0; p < W; p++)
     if (p != me) total_out += out_counts[p];
-  const int K     = exchange_chunk_count(static_cast<size_t>(total_out) * row_bytes);
+  const int K     = exchange_chunk_count(static_cast<size_t>(total_out) * row_bytes, chunks);
   cudaStream_t xs = comm->xchg_stream;
   auto cut        = [K](int64_t c, int k, int64_t* b, int64_t* n) {
     *b = c * k / K;
@@ -426,7 +427,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
           a.segments = seg, a.count = seg.total();
           launch_row_copy(a, stream);
         },
-        [](const list_segments&) {});
+        [](const list_segments&) {}, 1);
     }
     timer.mark("exchange");
     row_copy_args expand;  // rows[inverse[i]] -> output row i; ids nobody owns leave their row untouched

@@ -67,14 +67,17 @@ struct exchange_plan {
 // outgoing rows named by `segments` (array positions in out_buf's row numbering);
 // `unpack(segments)` consumes the incoming rows named by `segments`.  Every chunk is ONE NCCL
 // group over all peers on the communicator's exchange stream.  On return `stream` is ordered
-// after the last unpack.  The self segment (p == rank) is never touched.
+// after the last unpack.  The self segment (p == rank) is never touched.  `chunks` = 0 picks K
+// (4 above 16 MB of outgoing rows, else 1; WG_EXCHANGE_CHUNKS overrides either way); callers whose
+// pack and unpack do little pass 1, because then there is nothing to overlap and one large
+// exchange is fastest (measured at 8 GPUs: 2.21 ms with K = 1 against 2.29 ms with K = 4).
 struct list_segments;
 void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_counts,
                         const std::vector<int64_t>& out_displs, const std::vector<int64_t>& in_counts,
                         const std::vector<int64_t>& in_displs, char* out_buf, char* in_buf,
                         size_t row_bytes, cudaStream_t stream,
                         const std::function<void(const list_segments&)>& pack,
-                        const std::function<void(const list_segments&)>& unpack);
+                        const std::function<void(const list_segments&)>& unpack, int chunks = 0);
 
 struct cache_view;
 // Gather rows of a DISTRIBUTED table (descriptor `tab` over handle `h`) into `out`.  With
