@@ -44,6 +44,10 @@ def parse_args():
     ap.add_argument("--workload", default="auto", choices=["auto", "c2", "c3", "c4", "c5", "cache"])
     ap.add_argument("--rows", type=int, default=0, help="override the table rows (profiling on a small case)")
     ap.add_argument("--ids", type=int, default=0, help="override the ids per rank")
+    ap.add_argument("--env-sweep", default="",
+                    help="gather workloads: time the steps once per setting of the library's tuning variables, e.g. "
+                         "'WG_GATHER_DEDUP=1,WG_PEER_EXCHANGE=1;WG_GATHER_DEDUP=1,WG_PEER_EXCHANGE=0', one JSON line "
+                         "per setting (same value on every rank), instead of the bench line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -469,6 +473,29 @@ def main():
         t = torch.tensor([x], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.env_sweep:
+        # Tuning sweep: the library reads its WG_* variables at every call, so one process can
+        # compare settings on the same table and index batches.
+        for setting in args.env_sweep.split(";"):
+            pairs = dict(kv.split("=", 1) for kv in setting.split(",") if kv)
+            os.environ.update(pairs)
+            for i in range(args.warmup):
+                step(i)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(args.steps):
+                step(i)
+            e1.record()
+            barrier()
+            ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+            if rank == 0:
+                print(json.dumps({"variant": pairs, "workload": name, "n_gpus": world, "steps": args.steps,
+                                  "ms_per_step": ms,
+                                  "value": world * n_ids * ROW_DIM * es_out / (ms * 1e-3) / 1e9, "unit": "GB/s"}),
+                      flush=True)
+        return
 
     # ---- device-resident timing ------------------------------------------------------------
     for i in range(args.warmup):

@@ -353,6 +353,41 @@ def local_view(wg_tensor):
     return ptr, rows
 
 
+# ---- files ------------------------------------------------------------------------------------
+def load_wholegraph_handle_from_filelist(handle, memory_offset: int, memory_entry_size: int, file_entry_size: int,
+                                         round_robin_size: int, file_list: Sequence[str]) -> None:
+    """Collective: records of `file_entry_size` bytes from the files (taken as one sequence) into slots
+    `memory_entry_size` bytes apart, each rank loading its own shard; with round_robin_size > 0 blocks of that
+    many records are dealt to the ranks in turn."""
+    names = (C.c_char_p * len(file_list))(*[f.encode() for f in file_list])
+    check(lib().wholegraph_load_from_file(handle, memory_offset, memory_entry_size, file_entry_size, names,
+                                          len(file_list), round_robin_size), "wholegraph_load_from_file")
+
+
+def store_wholegraph_handle_to_file(handle, memory_offset: int, memory_entry_size: int, file_entry_size: int,
+                                    file_name: str) -> None:
+    """Collective: every rank writes the records of its shard to its own file."""
+    check(lib().wholegraph_store_to_file(handle, memory_offset, memory_entry_size, file_entry_size,
+                                         file_name.encode()), "wholegraph_store_to_file")
+
+
+def tensor_from_filelist(wg_tensor, file_list: Sequence[str], round_robin_size: int = 0) -> None:
+    """A 1-D or 2-D handle tensor (or a view of one) filled from files of dense rows."""
+    d = lib().wholegraph_tensor_get_tensor_description(wg_tensor).contents
+    es = lib().wholegraph_dtype_get_element_size(d.dtype)
+    row = es * (d.sizes[1] if d.dim == 2 else 1)
+    load_wholegraph_handle_from_filelist(C.c_void_p(lib().wholegraph_tensor_get_memory_handle(wg_tensor)),
+                                         d.storage_offset * es, es * d.strides[0], row, round_robin_size, file_list)
+
+
+def tensor_to_file(wg_tensor, file_name: str) -> None:
+    d = lib().wholegraph_tensor_get_tensor_description(wg_tensor).contents
+    es = lib().wholegraph_dtype_get_element_size(d.dtype)
+    row = es * (d.sizes[1] if d.dim == 2 else 1)
+    store_wholegraph_handle_to_file(C.c_void_p(lib().wholegraph_tensor_get_memory_handle(wg_tensor)),
+                                    d.storage_offset * es, es * d.strides[0], row, file_name)
+
+
 # ---- embeddings and sparse optimizers ------------------------------------------------------
 def create_embedding(desc: TensorDescription, comm, memory_type, memory_location, cache_policy=None,
                      entry_partition: Optional[Sequence[int]] = None, user_defined_sms: int = -1,

@@ -210,6 +210,47 @@ def main():
         if policy is not None:
             wgb.destroy_cache_policy(policy)
 
+    if scenario == "fileio":
+        # Plain layout: record r of the files is table row r.  Round robin: blocks of rr records are
+        # dealt to the ranks in turn (reference: file_io.cpp:100-200).  Every rank stores its shard.
+        rows, dim, rr = 1000 * world + 37, 12, 5
+        data = np.random.default_rng(9).integers(-2**31, 2**31 - 1, size=(rows, dim), dtype=np.int64).astype(np.int32)
+        files = [os.path.join(rdv, f"part_{k}.bin") for k in range(3)]
+        cuts = [0, rows // 3 + 1, rows // 3 + 2, rows]
+        if rank == 0:
+            for k in range(3):
+                data[cuts[k]:cuts[k + 1]].tofile(files[k])
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        for mem in (MT.MtContinuous, MT.MtDistributed, MT.MtChunked):
+            t, _ = make_table(mem, rows, dim, torch.int32)
+            wgb.tensor_from_filelist(t, files)
+            ids = torch.arange(rows, device="cuda", dtype=torch.int64)
+            got = torch.empty((rows, dim), dtype=torch.int32, device="cuda")
+            tu.gather(t, ids, got, env)
+            torch.cuda.synchronize()
+            assert np.array_equal(got.cpu().numpy(), data), f"plain load {mem.name} differs on rank {rank}"
+            out = os.path.join(rdv, f"stored_{mem.name}_{rank}.bin")
+            wgb.tensor_to_file(t, out)
+            off = orc.equal_partition_offsets(rows, world)
+            assert np.array_equal(np.fromfile(out, dtype=np.int32).reshape(-1, dim), data[off[rank]:off[rank + 1]])
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            wgb.destroy_wholegraph_tensor(t)
+        # round robin: every rank needs room for its share of the blocks
+        per_rank = rows // (world * rr) * rr + rr
+        t, _ = make_table(MT.MtDistributed, per_rank * world, dim, torch.int32)
+        wgb.tensor_from_filelist(t, files, rr)
+        extra = rows % (world * rr)
+        mine_n = rows // (world * rr) * rr + max(0, min(rr, extra - rank * rr))
+        j = np.arange(mine_n)
+        want = data[(j // rr * world + rank) * rr + j % rr]
+        local = tu.local_shard_as_torch(t)
+        torch.cuda.synchronize()
+        assert np.array_equal(local[:mine_n].cpu().numpy(), want), f"round-robin load differs on rank {rank}"
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        wgb.destroy_wholegraph_tensor(t)
+        wgb.destroy_communicator(comm)
+        print(f"rank {rank} ok", flush=True)
+        return
     if scenario == "cache":
         OT = wgb.WholeGraphOptimizerType
         rows = 128 * 8 * 5

@@ -19,7 +19,7 @@ def _device_count():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.parametrize("scenario", ["continuous", "distributed", "distributed-keepdups", "chunked", "optimizer", "optimizer-nopresum", "optimizer-peerpush", "cache"])
+@pytest.mark.parametrize("scenario", ["continuous", "distributed", "distributed-keepdups", "chunked", "optimizer", "optimizer-nopresum", "optimizer-peerpush", "cache", "fileio"])
 def test_multi_gpu_gather_scatter(scenario):
     world = min(_device_count(), int(os.environ.get("WG_TEST_WORLD", "8")))
     if world < 2:
