@@ -1,11 +1,13 @@
 // wholegraph_gather / wholegraph_scatter: argument checks, mapped (direct pointer) path and
-// the distributed (alltoallv) path.
+// the distributed path.
 //
 // Reference behaviour: cpp/src/wholegraph_tensor_ops/gather_op.cpp:12-106, scatter_op.cpp:12-98,
-// gather_op_impl_nccl.cu:23-171, scatter_op_impl_nccl.cu:23-170.  The distributed path here is
-// a W-step pipeline: at step s a rank gathers the rows its s-th neighbour asked for while the
-// rows of step s-1 are in flight on a second stream, and one host synchronisation (to learn
-// the per-rank counts) replaces the reference's three.
+// gather_op_impl_nccl.cu:23-171, scatter_op_impl_nccl.cu:23-170.  The distributed gather here
+// routes distinct ids only; one allgather gives every rank the whole count matrix and one host
+// synchronisation (NCCL needs host counts) replaces the reference's three.  Rows then travel
+// either by plain stores of the owner's gather kernel into the requester's region of a
+// peer-mapped arena, or, where that is not available, through NCCL in pipelined chunks on a
+// second stream.
 #include "ops.hpp"
 
 #include <algorithm>
