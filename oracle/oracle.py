@@ -261,3 +261,47 @@ def distributed_gather(shards: list[np.ndarray], offsets: np.ndarray, requests: 
             start += c
         outs.append(out)
     return outs
+
+
+class CachePolicyModel:
+    """Set-associative embedding cache, restated on the host: which rows of a table hold one of the
+    32 lines of their set after a sequence of access batches.
+
+    Geometry is the reference's (cpp/src/wholegraph/embedding_cache.hpp:64-74: sets of 32 lines,
+    a set covers `coverage` consecutive rows).  The replacement rule is the one this repository's
+    update kernel states, which satisfies what the reference's cache-set tests check
+    (cpp/tests/wholegraph_tensor_ops/cacheset_tests.cu:248-276: after an update no uncached row of
+    a touched set has a higher access count than a cached one; which of equal-count rows stay is
+    free): counters are exact; after a batch the cached rows of every touched set are the 32 with
+    the highest counters among (cached U accessed), cached rows first on ties, then lower row
+    numbers; rows that stay keep their line, new rows take the freed lines in priority order."""
+
+    SET_SIZE = 32
+
+    def __init__(self, rows: int, coverage: int):
+        assert rows % coverage == 0 and coverage >= self.SET_SIZE
+        self.count = np.zeros(rows, dtype=np.int64)
+        self.coverage = coverage
+        self.cached = {}          # set -> {row in set: line}
+
+    def update(self, ids: np.ndarray) -> None:
+        ids = np.asarray(ids, dtype=np.int64)
+        ids = ids[(ids >= 0) & (ids < self.count.shape[0])]
+        uniq, cnt = np.unique(ids, return_counts=True)
+        self.count[uniq] += cnt
+        for s in np.unique(uniq // self.coverage):
+            s = int(s)
+            lines = self.cached.setdefault(s, {})
+            touched = uniq[uniq // self.coverage == s] - s * self.coverage
+            cand = [(-(int(self.count[s * self.coverage + r]) * 2 + 1), int(r)) for r in lines]
+            cand += [(-(int(self.count[s * self.coverage + r]) * 2), int(r)) for r in touched if int(r) not in lines]
+            keep = [r for _, r in sorted(cand)[: self.SET_SIZE]]
+            free = sorted(set(range(self.SET_SIZE)) - {lines[r] for r in keep if r in lines})
+            new = {r: lines[r] for r in keep if r in lines}
+            for r in keep:
+                if r not in lines:
+                    new[r] = free.pop(0)
+            self.cached[s] = new
+
+    def lines_of(self, s: int) -> dict:
+        return self.cached.get(s, {})

@@ -6,8 +6,8 @@ The reference tests the same properties
 wholegraph_embedding_gradient_apply_tests.cu:798-1007): a cached embedding must return exactly
 what the uncached table holds, whatever the cache keeps, and after a write-back the table must
 hold what an uncached run would have produced.  The cache policy itself (which rows get the 32
-lines of a set) is checked against a model of the rule this library states: exact access
-counts, highest counts cached, cached rows win ties, then lower row numbers."""
+lines of a set) is checked against the oracle's host model of the rule this library states: exact
+access counts, highest counts cached, cached rows win ties, then lower row numbers."""
 import ctypes as C
 
 import numpy as np
@@ -62,36 +62,9 @@ def _forward(gpu, wgb, torch, emb, ids_np, dim, dtype, adjust):
     return out
 
 
-class PolicyModel:
-    """The stated update rule, per set: counters are exact; after a batch the cached rows of every
-    touched set are the 32 with the highest counters among (cached U accessed), cached rows first
-    on ties, then lower row numbers; rows that stay keep their line."""
-
-    def __init__(self, rows, coverage):
-        self.count = np.zeros(rows, dtype=np.int64)
-        self.coverage = coverage
-        self.cached = {}          # set -> {row in set: line}
-
-    def update(self, ids):
-        uniq, cnt = np.unique(ids, return_counts=True)
-        self.count[uniq] += cnt
-        for s in np.unique(uniq // self.coverage):
-            lines = self.cached.setdefault(int(s), {})
-            touched = uniq[uniq // self.coverage == s] - s * self.coverage
-            cand = [(-(self.count[s * self.coverage + r] * 2 + 1), r) for r in lines]
-            cand += [(-(self.count[s * self.coverage + r] * 2), int(r)) for r in touched if int(r) not in lines]
-            keep = [r for _, r in sorted(cand)[:32]]
-            free = sorted(set(range(32)) - {lines[r] for r in keep if r in lines})
-            new = {r: lines[r] for r in keep if r in lines}
-            for r in keep:                      # new rows take freed lines in priority order
-                if r not in lines:
-                    new[r] = free.pop(0)
-            self.cached[int(s)] = new
-
-
 @pytest.mark.parametrize("dtype_name,dim", [("f32", 32), ("f32", 13), ("f16", 64), ("bf16", 100)])
 @pytest.mark.parametrize("idx_dtype", [np.int32, np.int64])
-def test_cached_gather_returns_the_table_and_follows_the_policy(gpu, wgb, comm, dtype_name, dim, idx_dtype):
+def test_cached_gather_returns_the_table_and_follows_the_policy(gpu, wgb, orc, comm, dtype_name, dim, idx_dtype):
     import torch
     dtype = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[dtype_name]
     rows, ratio = 5000, 0.25                       # coverage 128 -> 40 sets of 32 lines, 5120 rows
@@ -104,7 +77,7 @@ def test_cached_gather_returns_the_table_and_follows_the_policy(gpu, wgb, comm, 
     init = torch.from_numpy(rng.uniform(-1, 1, size=(padded_rows, dim)).astype(np.float32)).cuda().to(dtype)
     gpu.scatter(init, torch.arange(padded_rows, device="cuda", dtype=torch.int64), table)
     torch.cuda.synchronize()
-    model = PolicyModel(padded_rows, coverage)
+    model = orc.CachePolicyModel(padded_rows, coverage)
     sets = padded_rows // coverage
 
     for step in range(6):

@@ -254,3 +254,34 @@ def test_two_level_gradient_sum_is_the_single_chain_up_to_rounding(orc):
     ua, sa = orc.dedup_gradients_by_rank(solo_ids, solo_g)
     ub, sb = orc.dedup_gradients(np.concatenate(solo_ids), np.concatenate(solo_g))
     assert np.array_equal(ua, ub) and np.array_equal(sa, sb)
+
+
+def test_cache_policy_model_keeps_the_reference_invariants(orc):
+    """What the reference's cache-set tests demand of an update (cacheset_tests.cu:248-276), checked on
+    the host model: at most 32 rows per set, lines are distinct, a row that stays keeps its line,
+    and no accessed-but-uncached row of a touched set has more accesses than a cached one."""
+    rng = np.random.default_rng(5)
+    rows, coverage = 64 * 40, 64
+    model = orc.CachePolicyModel(rows, coverage)
+    for step in range(12):
+        hot = rng.integers(0, rows // 8, size=1500)
+        ids = np.where(rng.random(1500) < 0.7, hot, rng.integers(0, rows, size=1500))
+        before = {s: dict(v) for s, v in model.cached.items()}
+        model.update(ids)
+        for s in np.unique(ids // coverage):
+            lines = model.lines_of(int(s))
+            assert 0 < len(lines) <= 32 and len(set(lines.values())) == len(lines)
+            assert all(0 <= l < 32 for l in lines.values())
+            for r, l in lines.items():
+                if r in before.get(int(s), {}):
+                    assert before[int(s)][r] == l
+            counts = model.count[s * coverage:(s + 1) * coverage]
+            cached_min = min(counts[r] for r in lines)
+            touched = np.unique(ids[ids // coverage == s]) - s * coverage
+            for r in touched:
+                if int(r) not in lines:
+                    assert counts[r] <= cached_min
+    # negative and out-of-range ids are ignored
+    total = model.count.sum()
+    model.update(np.array([-1, rows, rows + 5]))
+    assert model.count.sum() == total
