@@ -28,32 +28,48 @@ __device__ __forceinline__ int64_t load_id(const void* ids, int is64, int64_t i)
               : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
 }
 
-// One warp per id: lane l inspects line l of the id's set.
+// Four lanes per id, eight ids per warp: each lane of a group loads 16 bytes (8 tags) of the id's
+// 64-byte tag set and compares them; the group's answer is combined with two shuffles.  (One warp
+// per id, one tag per lane, spent 108 us on 1,048,576 ids whose tag sets sat in L2.)
+constexpr int kLookupLanes = 4;
+constexpr int kLookupIds   = 32 / kLookupLanes;
+
 __global__ void __launch_bounds__(kThreads) lookup_kernel(const void* ids, int is64, int64_t n, cache_view c,
                                                           int mark_modified, int64_t* row_address)
 {
   const int lane            = threadIdx.x & 31;
+  const int sub             = lane & (kLookupLanes - 1);  // which quarter of the tag set
+  const int slot            = lane / kLookupLanes;        // which of the warp's ids
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  for (int64_t i = warp_global; i < n; i += warp_stride) {
-    const int64_t local = load_id(ids, is64, i) - c.first_row;
-    if (local < 0 || local >= c.rows) {
-      if (lane == 0) row_address[i] = -1;
-      continue;
-    }
-    const int64_t set  = local / c.coverage;
-    const uint16_t row = static_cast<uint16_t>(local - set * c.coverage);
-    uint16_t* tag_ptr  = c.tags + set * kCacheSetSize + lane;
-    const uint16_t tag = *tag_ptr;
-    const bool hit     = (tag & kTagValid) != 0 && (tag & kTagRowMask) == row;
-    const unsigned m   = __ballot_sync(0xffffffffu, hit);
-    if (m != 0) {
-      const int line = __ffs(m) - 1;
-      if (lane == line) {
-        if (mark_modified) *tag_ptr = tag | kTagModified;
-        row_address[i] = reinterpret_cast<int64_t>(c.lines + (set * kCacheSetSize + line) * c.line_bytes);
+  for (int64_t base = warp_global * kLookupIds; base < n; base += warp_stride * kLookupIds) {
+    const int64_t i     = base + slot;
+    const bool live     = i < n;
+    const int64_t local = live ? load_id(ids, is64, i) - c.first_row : -1;
+    const bool in_range = live && local >= 0 && local < c.rows;
+    int64_t set         = 0;
+    int hit             = -1;
+    if (in_range) {
+      set                = local / c.coverage;
+      const uint32_t row = static_cast<uint32_t>(local - set * c.coverage);
+      const uint4 v      = *reinterpret_cast<const uint4*>(c.tags + set * kCacheSetSize + sub * 8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const uint32_t tag = (w[k >> 1] >> ((k & 1) * 16)) & 0xffffu;
+        if ((tag & kTagValid) != 0 && (tag & kTagRowMask) == row) hit = sub * 8 + k;
       }
-    } else if (lane == 0) {
+    }
+    hit = max(hit, __shfl_xor_sync(0xffffffffu, hit, 1));
+    hit = max(hit, __shfl_xor_sync(0xffffffffu, hit, 2));
+    if (sub != 0 || !live) continue;
+    if (!in_range) {
+      row_address[i] = -1;
+    } else if (hit >= 0) {
+      // equal ids in other groups may store the same value at the same time
+      if (mark_modified) c.tags[set * kCacheSetSize + hit] |= kTagModified;
+      row_address[i] = reinterpret_cast<int64_t>(c.lines + (set * kCacheSetSize + hit) * c.line_bytes);
+    } else {
       row_address[i] = reinterpret_cast<int64_t>(c.raw_rows + local * c.line_bytes);
     }
   }
@@ -304,6 +320,7 @@ void check_view(const cache_view& c)
   WGB_EXPECTS(c.rows % c.coverage == 0, "cached rows are not a multiple of the set coverage");
   WGB_EXPECTS(c.line_bytes % 16 == 0, "cache lines must be multiples of 16 bytes");
   WGB_EXPECTS(c.rows < (int64_t(1) << 32) - 1, "cached range too large");
+  WGB_EXPECTS(reinterpret_cast<uintptr_t>(c.tags) % 16 == 0, "cache tags must be 16-byte aligned");
 }
 
 }  // namespace
@@ -313,7 +330,7 @@ void cache_lookup(const void* ids, bool ids_are_64, int64_t n, const cache_view&
 {
   if (n == 0) return;
   check_view(c);
-  lookup_kernel<<<grid_for(n), kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, c, mark_modified ? 1 : 0,
+  lookup_kernel<<<grid_for((n + kLookupIds - 1) / kLookupIds), kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, c, mark_modified ? 1 : 0,
                                                       row_address);
   count_kernel_launch();
   WGB_LAUNCH_CHECK(stream);
