@@ -344,7 +344,9 @@ def run_cached_gather(args, torch, wgb, tu, comm):
                        "value_with_lfu_update": n * dim * 4 / (ms_adjust * 1e-3) / 1e9},
             "gpu_launches": int(launches), "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": how, "algorithmic_bytes_per_launch": algorithmic}}
+                         "traffic": None, "peak_source": how, "algorithmic_bytes_per_launch": algorithmic,
+                         "note": "row read + row written + id + one 64-byte tag set per id, no credit for repeats; the "
+                                 "hot rows of a Zipf list and their tag sets are served from L2, so this can exceed 1"}}
     print(json.dumps(line), flush=True)
     for w in wraps:
         wgb.destroy_wholegraph_tensor(w)
