@@ -205,6 +205,9 @@ def _declare(lib: C.CDLL) -> None:
         "wholegraph_embedding_get_optimizer_state": (vp, [vp, C.c_char_p]),
         "wholegraph_b200_embedding_get_cache_tensors": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
                                                                    C.POINTER(C.c_int)]),
+        "wholegraph_b200_release_output": (C.c_int, [vp]),
+        "graph_append_unique": (C.c_int, [vp, vp, vp, vp, C.POINTER(EnvFns), vp]),
+        "csr_add_self_loop": (C.c_int, [vp, vp, vp, vp, vp]),
         "wholegraph_embedding_writeback_cache": (C.c_int, [vp, i64]),
         "wholegraph_embedding_drop_all_cache": (C.c_int, [vp, i64]),
         "wholegraph_load_from_file": (C.c_int, [vp, sz, sz, sz, C.POINTER(C.c_char_p), C.c_int, C.c_int]),
@@ -351,6 +354,32 @@ def local_view(wg_tensor):
     rows = lib().wholegraph_tensor_get_tensor_description(lt).contents.sizes[0]
     destroy_wholegraph_tensor(lt)
     return ptr, rows
+
+
+# ---- graph utilities ---------------------------------------------------------------------------
+class OutputSlot(C.Structure):
+    """wholegraph_b200_output_slot_t: what the built-in output allocator hands back."""
+    _fields_ = [("pointer", C.c_void_p), ("description", TensorDescription)]
+
+
+def append_unique(target_nodes, neighbor_nodes, output_slot, output_neighbor_raw_to_unique_mapping, env_fns,
+                  stream_int: int = 0) -> None:
+    """Targets followed by the distinct neighbours that are not targets; `output_slot` (an OutputSlot when
+    env_fns is one of this library's allocators) receives the list, the optional mapping tensor the position
+    of every neighbour in it."""
+    check(lib().graph_append_unique(target_nodes, neighbor_nodes, C.byref(output_slot),
+                                    output_neighbor_raw_to_unique_mapping, env_fns, C.c_void_p(stream_int)),
+          "graph_append_unique")
+
+
+def release_output(output_slot) -> None:
+    """Free the buffer an OutputSlot received from this library's output allocator."""
+    check(lib().wholegraph_b200_release_output(C.byref(output_slot)), "wholegraph_b200_release_output")
+
+
+def add_csr_self_loop(csr_row_ptr, csr_col_ptr, output_csr_row_ptr, output_csr_col_ptr, stream_int: int = 0) -> None:
+    check(lib().csr_add_self_loop(csr_row_ptr, csr_col_ptr, output_csr_row_ptr, output_csr_col_ptr,
+                                  C.c_void_p(stream_int)), "csr_add_self_loop")
 
 
 # ---- files ------------------------------------------------------------------------------------

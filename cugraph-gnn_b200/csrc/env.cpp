@@ -1,5 +1,9 @@
 #include "env.hpp"
 
+#include <algorithm>
+
+#include <wholegraph/wholegraph_b200.h>
+
 #include <cuda_runtime_api.h>
 
 #include <cstdlib>
@@ -190,12 +194,18 @@ cache_pool& the_pool()
   return *p;
 }
 
-// Output memory: the "memory context" is a caller-owned slot that receives the pointer.
+// Output memory: the "memory context" is a caller-owned wholegraph_b200_output_slot_t that
+// receives the pointer and the description of what was allocated.
 void* output_malloc(wholegraph_tensor_description_t* d, wholegraph_memory_allocation_type_t where,
                     void* ctx, void*)
 {
-  void* p = raw_alloc(static_cast<size_t>(wholegraph_get_memory_size_from_tensor(d)), where);
-  if (ctx != nullptr) *static_cast<void**>(ctx) = p;
+  const size_t bytes = static_cast<size_t>(wholegraph_get_memory_size_from_tensor(d));
+  void* p            = raw_alloc(std::max<size_t>(bytes, 16), where);
+  if (ctx != nullptr) {
+    auto* slot        = static_cast<wholegraph_b200_output_slot_t*>(ctx);
+    slot->pointer     = p;
+    slot->description = *d;
+  }
   return p;
 }
 void output_free(void* ctx, void*)
@@ -222,6 +232,31 @@ wholegraph_env_func_t* wholegraph_b200_get_cached_env_func()
     {wgb::cached_create, wgb::cached_destroy, wgb::cached_malloc, wgb::cached_free, &wgb::the_pool()},
     {wgb::output_malloc, wgb::output_free, nullptr}};
   return &env;
+}
+
+wholegraph_error_code_t wholegraph_b200_release_output(wholegraph_b200_output_slot_t* slot)
+{
+  if (slot == nullptr) return WHOLEGRAPH_INVALID_INPUT;
+  if (slot->pointer != nullptr) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, slot->pointer) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return WHOLEGRAPH_CUDA_ERROR;
+    }
+    cudaError_t e = cudaSuccess;
+    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged)
+      e = cudaFree(slot->pointer);
+    else if (attr.type == cudaMemoryTypeHost)
+      e = cudaFreeHost(slot->pointer);
+    else
+      free(slot->pointer);  // pageable host memory of WHOLEGRAPH_MA_HOST
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return WHOLEGRAPH_CUDA_ERROR;
+    }
+  }
+  slot->pointer = nullptr;
+  return WHOLEGRAPH_SUCCESS;
 }
 
 void wholegraph_b200_drop_cached_env_func_memory()

@@ -1,8 +1,7 @@
-// Entry points of the reference ABI that lie outside the embedding path (graph sampling,
-// append-unique, self loops; cpp/include/wholegraph/wholegraph_op.h, graph_op.h).  They are
+// Entry points of the reference ABI that lie outside the embedding path (graph sampling and the
+// host restatements of its random streams; cpp/include/wholegraph/wholegraph_op.h).  They are
 // exported so that bindings built against the reference's headers resolve every symbol, and they
 // refuse loudly: nothing is computed, on any device or on the host.
-#include <wholegraph/graph_op.h>
 #include <wholegraph/wholegraph_op.h>
 
 #include "common.hpp"
@@ -39,18 +38,6 @@ wholegraph_error_code_t generate_random_positive_int_cpu(int64_t, int64_t, whole
 wholegraph_error_code_t generate_exponential_distribution_negative_float_cpu(int64_t, int64_t, wholegraph_tensor_t)
 {
   return refuse("generate_exponential_distribution_negative_float_cpu");
-}
-
-wholegraph_error_code_t graph_append_unique(wholegraph_tensor_t, wholegraph_tensor_t, void*, wholegraph_tensor_t,
-                                            wholegraph_env_func_t*, void*)
-{
-  return refuse("graph_append_unique");
-}
-
-wholegraph_error_code_t csr_add_self_loop(wholegraph_tensor_t, wholegraph_tensor_t, wholegraph_tensor_t,
-                                          wholegraph_tensor_t, void*)
-{
-  return refuse("csr_add_self_loop");
 }
 
 }  // extern "C"

@@ -10,6 +10,7 @@
 
 #include <wholegraph/embedding.h>
 #include <wholegraph/env_func_ptrs.h>
+#include <wholegraph/tensor_description.h>
 #include <wholegraph/wholegraph.h>
 #include <wholegraph/wholegraph_tensor.h>
 
@@ -117,6 +118,21 @@ wholegraph_error_code_t wholegraph_b200_embedding_get_cache_tensors(wholegraph_e
                                                                       wholegraph_tensor_t* lfu,
                                                                       wholegraph_tensor_t* lines,
                                                                       int* set_coverage);
+
+/* Memory context for the output allocator of the two built-in env functions above: an op that
+ * produces an output of a size only it knows (graph_append_unique) calls
+ * env->output_fns.malloc_fn with the caller's context pointer, and these allocators fill the slot
+ * with the device pointer and the description (dtype, length) of what they allocated.  The caller
+ * owns the buffer and releases it with wholegraph_b200_release_output.  Callers with their own allocator pass whatever
+ * context their own malloc_fn expects, as with the reference. */
+typedef struct wholegraph_b200_output_slot_t {
+  void* pointer;
+  wholegraph_tensor_description_t description;
+} wholegraph_b200_output_slot_t;
+
+/* Release the buffer of a slot filled by the built-in output allocator (cudaFree, cudaFreeHost or free,
+ * by where it was allocated) and clear the slot.  Other kinds of context must not be passed. */
+wholegraph_error_code_t wholegraph_b200_release_output(wholegraph_b200_output_slot_t* slot);
 
 /* Number of kernels this library has launched in this process since load. */
 unsigned long long wholegraph_b200_kernel_launch_count();

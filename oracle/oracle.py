@@ -305,3 +305,34 @@ class CachePolicyModel:
 
     def lines_of(self, s: int) -> dict:
         return self.cached.get(s, {})
+
+
+def append_unique(targets: np.ndarray, neighbors: np.ndarray):
+    """(unique nodes, mapping) of the append-unique step: the targets in their order, then every
+    distinct neighbour that is not a target, ascending; mapping[j] = position of neighbors[j] in
+    that list (a neighbour equal to several targets maps to the first of them).
+
+    The reference guarantees the same except for the order of the appended neighbours, which is the
+    order of its hash table (cpp/src/graph_ops/append_unique_func.cuh:263-341)."""
+    targets, neighbors = np.asarray(targets), np.asarray(neighbors)
+    first = {}
+    for i, t in enumerate(targets.tolist()):
+        first.setdefault(t, i)
+    new = sorted(set(neighbors.tolist()) - set(first))
+    where = dict(first)
+    where.update({v: len(targets) + k for k, v in enumerate(new)})
+    unique = np.concatenate([targets, np.asarray(new, dtype=targets.dtype)]) if len(new) else targets.copy()
+    mapping = np.asarray([where[v] for v in neighbors.tolist()], dtype=np.int32)
+    return unique, mapping
+
+
+def csr_add_self_loop(row_ptr: np.ndarray, col: np.ndarray):
+    """CSR with edge (r, r) put first in every row (cpp/src/graph_ops/csr_add_self_loop_func.cuh:13-32)."""
+    row_ptr, col = np.asarray(row_ptr, dtype=np.int32), np.asarray(col, dtype=np.int32)
+    rows = len(row_ptr) - 1
+    out_ptr = (row_ptr + np.arange(rows + 1, dtype=np.int32)).astype(np.int32)
+    out_col = np.empty(len(col) + rows, dtype=np.int32)
+    for r in range(rows):
+        out_col[out_ptr[r]] = r
+        out_col[out_ptr[r] + 1:out_ptr[r + 1]] = col[row_ptr[r]:row_ptr[r + 1]]
+    return out_ptr, out_col

@@ -285,3 +285,20 @@ def test_cache_policy_model_keeps_the_reference_invariants(orc):
     total = model.count.sum()
     model.update(np.array([-1, rows, rows + 5]))
     assert model.count.sum() == total
+
+
+def test_graph_utilities_of_the_oracle(orc):
+    """append-unique and self loops on the host: the properties the reference's tests check."""
+    rng = np.random.default_rng(2)
+    targets = rng.permutation(500)[:60].astype(np.int64)
+    neighbors = rng.integers(0, 500, size=2000).astype(np.int64)
+    unique, mapping = orc.append_unique(targets, neighbors)
+    assert np.array_equal(unique[:60], targets) and len(np.unique(unique)) == len(unique)
+    assert set(unique.tolist()) == set(targets.tolist()) | set(neighbors.tolist())
+    assert np.array_equal(unique[mapping], neighbors) and mapping.dtype == np.int32
+    assert np.all(np.diff(unique[60:]) > 0)
+    row_ptr = np.array([0, 2, 2, 5], dtype=np.int32)
+    col = np.array([1, 2, 0, 1, 2], dtype=np.int32)
+    out_ptr, out_col = orc.csr_add_self_loop(row_ptr, col)
+    assert out_ptr.tolist() == [0, 3, 4, 8]
+    assert out_col.tolist() == [0, 1, 2, 1, 2, 0, 1, 2]
