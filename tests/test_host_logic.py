@@ -67,3 +67,45 @@ def test_cache_policy_ratio_bounds(wgb):
     assert lib.wholegraph_create_embedding_cache_policy(C.byref(p), None, 1, 1, 1, C.c_float(1.5)) == int(wgb.ErrorCode.INVALID_VALUE)
     assert lib.wholegraph_create_embedding_cache_policy(C.byref(p), None, 1, 1, 1, C.c_float(0.1)) == 0
     assert lib.wholegraph_destroy_embedding_cache_policy(p) == 0
+
+
+def _fake_tensor(wgb, sizes, dtype, address=0x10000):
+    """A descriptor-only tensor over an address that is never dereferenced: argument checks only."""
+    return wgb.make_tensor_from_pointer(address, wgb.make_description(sizes, dtype))
+
+
+def test_graph_utilities_check_their_arguments_before_any_device_work(wgb):
+    lib, DT, E = wgb.lib(), wgb.WholeGraphDataType, wgb.ErrorCode
+    i32 = _fake_tensor(wgb, [8], DT.DtInt)
+    i64 = _fake_tensor(wgb, [8], DT.DtInt64)
+    f32 = _fake_tensor(wgb, [8], DT.DtFloat)
+    m2d = _fake_tensor(wgb, [4, 2], DT.DtInt)
+    env = wgb.default_env_fns() if hasattr(wgb, "default_env_fns") else wgb.cached_env_fns()
+    slot = wgb.OutputSlot()
+    # append unique: 1-D ids of one integer type, int32 mapping
+    assert lib.graph_append_unique(m2d, i32, C.byref(slot), None, env, None) == int(E.INVALID_INPUT)
+    assert lib.graph_append_unique(i32, m2d, C.byref(slot), None, env, None) == int(E.INVALID_INPUT)
+    assert lib.graph_append_unique(i32, i64, C.byref(slot), None, env, None) == int(E.LOGIC_ERROR)
+    assert lib.graph_append_unique(f32, f32, C.byref(slot), None, env, None) == int(E.INVALID_INPUT)
+    assert lib.graph_append_unique(i64, i64, C.byref(slot), i64, env, None) == int(E.INVALID_INPUT)   # mapping not int32
+    assert lib.graph_append_unique(None, i64, C.byref(slot), None, env, None) == int(E.INVALID_INPUT)
+    assert slot.pointer is None
+    # self loops: four 1-D int32 tensors, outputs large enough
+    small = _fake_tensor(wgb, [3], DT.DtInt)
+    assert lib.csr_add_self_loop(i64, i32, i32, i32, None) == int(E.INVALID_INPUT)
+    assert lib.csr_add_self_loop(i32, m2d, i32, i32, None) == int(E.INVALID_INPUT)
+    assert lib.csr_add_self_loop(i32, i32, small, i32, None) == int(E.INVALID_INPUT)                  # 8 row pointers need 8
+    assert lib.csr_add_self_loop(i32, i32, i32, i32, None) == int(E.INVALID_INPUT)                    # 8 + 7 columns needed
+    for t in (i32, i64, f32, m2d, small):
+        wgb.destroy_wholegraph_tensor(t)
+    assert lib.wholegraph_b200_release_output(None) == int(E.INVALID_INPUT)
+    assert lib.wholegraph_b200_release_output(C.byref(slot)) == 0                                      # empty slot: nothing to free
+
+
+def test_sampling_entry_points_refuse(wgb):
+    lib = wgb.lib()
+    for name in ("wholegraph_csr_unweighted_sample_without_replacement", "wholegraph_csr_weighted_sample_without_replacement",
+                 "generate_random_positive_int_cpu", "generate_exponential_distribution_negative_float_cpu"):
+        assert hasattr(lib, name)
+    lib.generate_random_positive_int_cpu.argtypes = [C.c_int64, C.c_int64, C.c_void_p]
+    assert lib.generate_random_positive_int_cpu(1, 0, None) == int(wgb.ErrorCode.NOT_IMPLEMENTED)
