@@ -220,6 +220,9 @@ void cached_gather(wholegraph_embedding_* e, wholegraph_tensor_t indices, wholeg
   const bool ids_are_64 = id->dtype == WHOLEGRAPH_DT_INT64;
   const void* ids       = wholegraph_tensor_get_data_pointer(indices);
   void* out             = wholegraph_tensor_get_data_pointer(output);
+  WGB_EXPECTS(n == 0 || (ids != nullptr && out != nullptr), "indices and output must be device buffers");
+  // The copy launchers add the storage offset themselves: hand them the start of the storage.
+  if (out != nullptr) out = static_cast<char*>(out) - od.storage_offset * wholegraph_dtype_get_element_size(od.dtype);
   wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(e->allocated);
   auto* comm            = e->comm;
   const cache_view mine = local_cache_of(e);

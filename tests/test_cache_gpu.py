@@ -159,3 +159,30 @@ def test_training_through_the_cache_matches_the_oracle(gpu, wgb, orc, comm, opt_
     MT = wgb.WholeGraphMemoryType
     _run(gpu, wgb, orc, comm, opt_name, rows=3000, dim=dim, table_dtype=table_dtype, idx_dtype=np.int64,
          steps=5, n=2000, params=params, mem_type=MT.MtContinuous, cache_ratio=0.125)
+
+
+def test_cached_gather_into_an_output_view_with_a_storage_offset(gpu, wgb, comm):
+    """The output may be a strided view that starts some elements into its storage: only the viewed
+    elements are written."""
+    import torch
+    rows, dim, n, offset, stride = 1024, 16, 300, 40, 24
+    emb, policy = _make(gpu, wgb, comm, rows, dim, torch.float32, 0.5)
+    table = wgb.embedding_tensor(emb)
+    init = torch.arange(rows * dim, device="cuda", dtype=torch.float32).reshape(rows, dim)
+    gpu.scatter(init, torch.arange(rows, device="cuda", dtype=torch.int64), table)
+    ids = torch.randint(0, rows, (n,), device="cuda", dtype=torch.int64)
+    storage = torch.empty(offset + n * stride, device="cuda", dtype=torch.float32)
+    odesc = wgb.make_description([n, dim], wgb.WholeGraphDataType.DtFloat, strides=[stride, 1], storage_offset=offset)
+    wo = wgb.make_tensor_from_pointer(storage.data_ptr(), odesc)
+    wi = gpu.wrap_torch_tensor(ids)
+    for adjust in (True, False, True):
+        storage.fill_(-1.0)
+        wgb.EmbeddingGatherForward(emb, wi, wo, adjust, wgb.cached_env_fns(), gpu.current_stream_int())
+        torch.cuda.synchronize()
+        got = storage[offset:].reshape(n, stride)
+        assert torch.equal(got[:, :dim], init[ids])
+        assert bool((got[:, dim:] == -1.0).all()) and bool((storage[:offset] == -1.0).all())
+    wgb.destroy_wholegraph_tensor(wo)
+    wgb.destroy_wholegraph_tensor(wi)
+    wgb.destroy_embedding(emb)
+    wgb.destroy_cache_policy(policy)
