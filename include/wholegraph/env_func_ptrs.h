@@ -1,10 +1,17 @@
 /*
  * wholegraph-b200: caller-supplied allocator callbacks.
  *
- * ABI mirror of the reference's cpp/include/wholegraph/env_func_ptrs.h:17-62.
- * Every temporary an op needs is requested through `temporary_fns`:
- *   create_memory_context -> malloc(desc, DEVICE|HOST|PINNED) -> free -> destroy_memory_context.
- * One context owns at most one buffer.
+ * ABI mirror of the reference's cpp/include/wholegraph/env_func_ptrs.h:17-62 (same type and member
+ * names, same layouts).  How the library uses them:
+ *
+ *   scratch   env->temporary_fns: create_memory_context_fn(&ctx, global) once per buffer, then
+ *             malloc_fn(&description, where, ctx, global) exactly once for that context, later
+ *             free_fn(ctx, global) and destroy_memory_context_fn(ctx, global).  One context owns
+ *             at most one buffer; `where` says device, pageable host or pinned host memory.
+ *   outputs   env->output_fns: for results whose size only the op knows, malloc_fn is called with
+ *             the context pointer the caller passed to the op; the buffer belongs to the caller.
+ *
+ * The library's own allocators (wholegraph_b200.h) are instances of these tables.
  */
 #pragma once
 
@@ -15,27 +22,23 @@
 extern "C" {
 #endif
 
+/* Where a requested buffer must live. */
 enum wholegraph_memory_allocation_type_t {
   WHOLEGRAPH_MA_NONE = 0,
-  WHOLEGRAPH_MA_DEVICE,
-  WHOLEGRAPH_MA_HOST,
-  WHOLEGRAPH_MA_PINNED,
+  WHOLEGRAPH_MA_DEVICE,  /* 1: device memory */
+  WHOLEGRAPH_MA_HOST,    /* 2: pageable host memory */
+  WHOLEGRAPH_MA_PINNED,  /* 3: page-locked host memory */
 };
 
-typedef void (*wholegraph_create_memory_context_func_t)(void** memory_context,
-                                                         void* global_context);
+/* ctx_out receives a new context; user is the table's global_context. */
+typedef void (*wholegraph_create_memory_context_func_t)(void** ctx_out, void* user);
+typedef void (*wholegraph_destroy_memory_context_func_t)(void* ctx, void* user);
+/* Returns the buffer for a tensor of the given description (element count x element size bytes). */
+typedef void* (*wholegraph_malloc_func_t)(wholegraph_tensor_description_t* what,
+                                           wholegraph_memory_allocation_type_t where, void* ctx, void* user);
+typedef void (*wholegraph_free_func_t)(void* ctx, void* user);
 
-typedef void (*wholegraph_destroy_memory_context_func_t)(void* memory_context,
-                                                          void* global_context);
-
-typedef void* (*wholegraph_malloc_func_t)(
-  wholegraph_tensor_description_t* desc,
-  wholegraph_memory_allocation_type_t memory_allocation_type,
-  void* memory_context,
-  void* global_context);
-
-typedef void (*wholegraph_free_func_t)(void* memory_context, void* global_context);
-
+/* Scratch buffers of one op call. */
 struct wholegraph_temp_memory_func_t {
   wholegraph_create_memory_context_func_t create_memory_context_fn;
   wholegraph_destroy_memory_context_func_t destroy_memory_context_fn;
@@ -44,6 +47,7 @@ struct wholegraph_temp_memory_func_t {
   void* global_context;
 };
 
+/* Variable-size op outputs. */
 struct wholegraph_output_memory_func_t {
   wholegraph_malloc_func_t malloc_fn;
   wholegraph_free_func_t free_fn;
@@ -51,11 +55,12 @@ struct wholegraph_output_memory_func_t {
 };
 
 struct wholegraph_env_func_t {
-  wholegraph_temp_memory_func_t temporary_fns; /* scratch buffers of one op call */
-  wholegraph_output_memory_func_t output_fns;  /* variable-size op outputs */
+  wholegraph_temp_memory_func_t temporary_fns;
+  wholegraph_output_memory_func_t output_fns;
 };
 
-/* Cached cudaDeviceProp of a device (env_func_ptrs.h:64). */
+/* Properties of device `dev_id` (the current device when negative), queried once and cached
+ * (reference: env_func_ptrs.h:64). */
 cudaDeviceProp* get_device_prop(int dev_id);
 
 #ifdef __cplusplus

@@ -2,7 +2,7 @@
  * Graph utility entry points of the WholeGraph C ABI
  * (reference: cpp/include/wholegraph/graph_op.h:27-48).
  *
- * Same declarations, argument checks and return codes.  One stated difference in
+ * Same functions, argument order, checks and return codes.  One stated difference in
  * graph_append_unique: the reference appends the new neighbours in the order its hash table
  * happens to hold them; here they are appended in ascending id order, so results are reproducible.
  */
@@ -17,26 +17,20 @@ extern "C" {
 #endif
 
 /* Node list of a sampled hop: the target nodes in their order, then every distinct neighbour that is
- * not a target (ascending).  The list is allocated through env->output_fns for
- * output_unique_node_memory_context once its length is known; the optional int32 mapping tensor
- * receives, per neighbour, its position in the list.  Ids are int32 or int64 (same type for both
- * inputs), tensors 1-D and dense.  Synchronises the stream; outputs are complete on return. */
-wholegraph_error_code_t graph_append_unique(
-  wholegraph_tensor_t target_nodes_tensor,
-  wholegraph_tensor_t neighbor_nodes_tensor,
-  void* output_unique_node_memory_context,
-  wholegraph_tensor_t output_neighbor_raw_to_unique_mapping_tensor,
-  wholegraph_env_func_t* p_env_fns,
-  void* stream);
+ * not a target (ascending).  The list is allocated through env->output_fns for `unique_nodes_context`
+ * once its length is known; the optional int32 tensor `neighbour_positions` receives, per neighbour,
+ * its position in the list.  Ids are int32 or int64 (same type for both inputs), tensors 1-D and
+ * dense.  Synchronises the stream; outputs are complete on return. */
+wholegraph_error_code_t graph_append_unique(wholegraph_tensor_t targets, wholegraph_tensor_t neighbours,
+                                            void* unique_nodes_context, wholegraph_tensor_t neighbour_positions,
+                                            wholegraph_env_func_t* env, void* stream);
 
-/* CSR graph (int32 row pointers and columns) with edge (r, r) put first in every row r:
- * output_row_ptr[r] = row_ptr[r] + r.  The outputs must hold rows + 1 and edges + rows entries.
- * Asynchronous on the stream. */
-wholegraph_error_code_t csr_add_self_loop(wholegraph_tensor_t csr_row_ptr_tensor,
-                                           wholegraph_tensor_t csr_col_ptr_tensor,
-                                           wholegraph_tensor_t output_csr_row_ptr_tensor,
-                                           wholegraph_tensor_t output_csr_col_ptr_tensor,
-                                           void* stream);
+/* CSR graph (int32 row offsets and column ids) with edge (r, r) put first in every row r:
+ * looped_row_offsets[r] = row_offsets[r] + r.  The outputs must hold rows + 1 and edges + rows
+ * entries.  Asynchronous on the stream. */
+wholegraph_error_code_t csr_add_self_loop(wholegraph_tensor_t row_offsets, wholegraph_tensor_t column_ids,
+                                          wholegraph_tensor_t looped_row_offsets,
+                                          wholegraph_tensor_t looped_column_ids, void* stream);
 
 #ifdef __cplusplus
 }

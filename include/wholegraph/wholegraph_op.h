@@ -18,42 +18,27 @@
 extern "C" {
 #endif
 
-/* Neighbour sampling without replacement on a CSR graph held in WholeGraph tensors; outputs go to
- * caller memory contexts through env->output_fns. */
+/* Neighbour sampling without replacement on a CSR graph held in WholeGraph tensors (row offsets,
+ * column ids), at most `fanout` neighbours per centre node.  Offsets per centre go to
+ * `sample_offsets`; sampled neighbours, their centre's position and the edge ids go to caller
+ * memory contexts through env->output_fns. */
 wholegraph_error_code_t wholegraph_csr_unweighted_sample_without_replacement(
-  wholegraph_tensor_t wg_csr_row_ptr_tensor,
-  wholegraph_tensor_t wg_csr_col_ptr_tensor,
-  wholegraph_tensor_t center_nodes_tensor,
-  int max_sample_count,
-  wholegraph_tensor_t output_sample_offset_tensor,
-  void* output_dest_memory_context,
-  void* output_center_localid_memory_context,
-  void* output_edge_gid_memory_context,
-  unsigned long long random_seed,
-  wholegraph_env_func_t* p_env_fns,
-  void* stream);
+  wholegraph_tensor_t row_offsets, wholegraph_tensor_t column_ids, wholegraph_tensor_t centres, int fanout,
+  wholegraph_tensor_t sample_offsets, void* neighbours_context, void* centre_position_context,
+  void* edge_id_context, unsigned long long seed, wholegraph_env_func_t* env, void* stream);
 
-/* The same with per-edge weights. */
+/* The same with one weight per edge (`edge_weights`, laid out like `column_ids`). */
 wholegraph_error_code_t wholegraph_csr_weighted_sample_without_replacement(
-  wholegraph_tensor_t wg_csr_row_ptr_tensor,
-  wholegraph_tensor_t wg_csr_col_ptr_tensor,
-  wholegraph_tensor_t wg_csr_weight_ptr_tensor,
-  wholegraph_tensor_t center_nodes_tensor,
-  int max_sample_count,
-  wholegraph_tensor_t output_sample_offset_tensor,
-  void* output_dest_memory_context,
-  void* output_center_localid_memory_context,
-  void* output_edge_gid_memory_context,
-  unsigned long long random_seed,
-  wholegraph_env_func_t* p_env_fns,
+  wholegraph_tensor_t row_offsets, wholegraph_tensor_t column_ids, wholegraph_tensor_t edge_weights,
+  wholegraph_tensor_t centres, int fanout, wholegraph_tensor_t sample_offsets, void* neighbours_context,
+  void* centre_position_context, void* edge_id_context, unsigned long long seed, wholegraph_env_func_t* env,
   void* stream);
 
-/* Host-side restatements of the sampler's random streams, used by the reference's tests. */
-wholegraph_error_code_t generate_random_positive_int_cpu(int64_t random_seed,
-                                                          int64_t subsequence,
-                                                          wholegraph_tensor_t output);
-wholegraph_error_code_t generate_exponential_distribution_negative_float_cpu(
-  int64_t random_seed, int64_t subsequence, wholegraph_tensor_t output);
+/* Host-side restatements of the sampler's random streams (positive integers; negated
+ * exponential variates), used by the reference's tests: `out` is a 1-D host tensor. */
+wholegraph_error_code_t generate_random_positive_int_cpu(int64_t seed, int64_t subsequence, wholegraph_tensor_t out);
+wholegraph_error_code_t generate_exponential_distribution_negative_float_cpu(int64_t seed, int64_t subsequence,
+                                                                             wholegraph_tensor_t out);
 
 #ifdef __cplusplus
 }
