@@ -187,6 +187,11 @@ def _declare(lib: C.CDLL) -> None:
                                                          vp, vp, vp, vp, vp]),
         "wholegraph_b200_partition_by_owner_no_alloc": (C.c_int, [vp, C.c_int, i64, C.POINTER(i64), C.c_int,
                                                                   vp, vp, vp, vp, vp]),
+        "wholegraph_b200_unique_workspace_bytes": (sz, [i64, i64]),
+        "wholegraph_b200_unique_by_owner": (C.c_int, [vp, C.c_int, i64, C.POINTER(i64), C.c_int, vp, sz,
+                                                      vp, vp, vp, vp, vp]),
+        "wholegraph_b200_exchange_chunk_count": (C.c_int, [C.POINTER(i64), C.c_int, sz, C.c_int, C.c_int]),
+        "wholegraph_b200_reload_tuning": (C.c_int, [vp]),
         "wholegraph_b200_version": (C.c_char_p, []),
     }
     optional = {

@@ -14,6 +14,8 @@
 #include "handle.hpp"
 #include "kernels/partition.hpp"
 #include "kernels/row_copy.hpp"
+#include "kernels/unique_ids.hpp"
+#include "ops.hpp"
 
 static bool g_inited = false;
 
@@ -387,6 +389,55 @@ wholegraph_error_code_t wholegraph_b200_partition_by_owner_no_alloc(const void* 
                                           static_cast<cudaStream_t>(stream));
   return WHOLEGRAPH_SUCCESS;
   WGB_API_END("wholegraph_b200_partition_by_owner_no_alloc")
+}
+
+size_t wholegraph_b200_unique_workspace_bytes(int64_t n, int64_t total_rows)
+{
+  return wgb::unique_workspace_bytes(n, total_rows);
+}
+
+wholegraph_error_code_t wholegraph_b200_unique_by_owner(const void* ids,
+                                                          int ids_are_64,
+                                                          int64_t n,
+                                                          const int64_t* first_row,
+                                                          int world,
+                                                          void* workspace,
+                                                          size_t workspace_bytes,
+                                                          int64_t* unique_ids,
+                                                          int64_t* inverse,
+                                                          int64_t* counts,
+                                                          int64_t* starts,
+                                                          void* stream)
+{
+  if (n < 0 || first_row == nullptr || counts == nullptr || starts == nullptr)
+    return WHOLEGRAPH_INVALID_INPUT;
+  if (n > 0 && (ids == nullptr || workspace == nullptr || unique_ids == nullptr || inverse == nullptr))
+    return WHOLEGRAPH_INVALID_INPUT;
+  if (world < 1 || world > wgb::kMaxPartitionRanks) return WHOLEGRAPH_INVALID_VALUE;
+  WGB_API_BEGIN
+  wgb::check_owner_table(first_row, world);
+  if (!wgb::unique_supported(n, first_row[world])) return WHOLEGRAPH_INVALID_VALUE;
+  if (workspace_bytes < wgb::unique_workspace_bytes(n, first_row[world])) return WHOLEGRAPH_INVALID_VALUE;
+  wgb::unique_by_owner(ids, ids_are_64 != 0, n, first_row, world, workspace, unique_ids, inverse, counts,
+                       starts, static_cast<cudaStream_t>(stream));
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_b200_unique_by_owner")
+}
+
+int wholegraph_b200_exchange_chunk_count(const int64_t* matrix, int world, size_t row_bytes, int wanted,
+                                         int forced)
+{
+  if (matrix == nullptr || world < 1) return 1;
+  return wgb::exchange_chunk_count(matrix, world, row_bytes, wanted, forced);
+}
+
+wholegraph_error_code_t wholegraph_b200_reload_tuning(wholegraph_comm_t comm)
+{
+  if (comm == nullptr) return WHOLEGRAPH_INVALID_INPUT;
+  WGB_API_BEGIN
+  comm->reload_tuning();
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_b200_reload_tuning")
 }
 
 unsigned long long wholegraph_b200_kernel_launch_count() { return wgb::kernel_launch_count(); }

@@ -4,6 +4,7 @@
 #include <nccl.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <memory>
@@ -107,6 +108,24 @@ void setup_staging(wholegraph_comm_* c)
 
 }  // namespace
 
+exchange_tuning tuning_from_environment()
+{
+  auto flag = [](const char* name, int otherwise) {
+    const char* e = getenv(name);
+    if (e == nullptr || e[0] == '\0') return otherwise;
+    return e[0] == '0' ? 0 : 1;
+  };
+  exchange_tuning t;
+  t.peer_exchange   = flag("WG_PEER_EXCHANGE", t.peer_exchange);
+  t.gather_dedup    = flag("WG_GATHER_DEDUP", t.gather_dedup);
+  t.gradient_presum = flag("WG_GRADIENT_PRESUM", t.gradient_presum);
+  t.peer_gradient   = flag("WG_PEER_GRADIENT", t.peer_gradient);
+  t.sync_free       = flag("WG_SYNC_FREE", t.sync_free);
+  const char* k     = getenv("WG_EXCHANGE_CHUNKS");
+  t.exchange_chunks = k != nullptr ? std::min(std::max(0, atoi(k)), 16) : 0;
+  return t;
+}
+
 void nccl_get_unique_id(wholegraph_unique_id_t* id)
 {
   static_assert(sizeof(ncclUniqueId) <= WHOLEGRAPH_UNIQUE_ID_BYTES, "unique id too small");
@@ -132,6 +151,7 @@ wholegraph_comm_* create_comm(const wholegraph_unique_id_t& id, int rank, int si
     c->nccl = nc;
   }
   setup_staging(c.get());
+  c->reload_tuning();
   wholegraph_comm_* raw = c.release();
   {
     std::lock_guard<std::mutex> lk(g_comm_mu);
@@ -172,6 +192,7 @@ wholegraph_comm_* split_comm(wholegraph_comm_* comm, int color, int key)
     nccl_lib().CommDestroy(nc);
   }
   setup_staging(c.get());
+  c->reload_tuning();
   wholegraph_comm_* raw = c.release();
   {
     std::lock_guard<std::mutex> lk(g_comm_mu);
@@ -229,6 +250,18 @@ cudaEvent_t wholegraph_comm_::event(size_t i)
     events.push_back(e);
   }
   return events[i];
+}
+
+void wholegraph_comm_::reload_tuning()
+{
+  const wgb::exchange_tuning mine = wgb::tuning_from_environment();
+  // The reference checks the parameters of every collective call the same way
+  // (wg_comm_check_all_same, cpp/src/wholegraph/communicator.hpp:220-249).
+  if (!all_same(&mine, sizeof(mine)))
+    throw wgb::logic_error(
+      "the WG_* tuning variables differ between the ranks of a communicator; they select which "
+      "collectives an op issues and must be equal everywhere");
+  tuning = mine;
 }
 
 void wholegraph_comm_::check_async_error()

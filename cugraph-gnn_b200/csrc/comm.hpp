@@ -15,6 +15,23 @@
 
 struct wholegraph_handle_;
 
+namespace wgb {
+
+// Switches of the distributed ops, read from the environment when a communicator is created
+// (and again by reload_tuning).  Every rank of a communicator must hold the same values, because
+// they select which collectives an op issues; creation checks that.
+struct exchange_tuning {
+  int peer_exchange   = 1;  // WG_PEER_EXCHANGE=0: rows travel by NCCL instead of peer stores
+  int gather_dedup    = 1;  // WG_GATHER_DEDUP=0: duplicates are routed as they are
+  int gradient_presum = 1;  // WG_GRADIENT_PRESUM=0: every gradient row goes to its owner
+  int peer_gradient   = 0;  // WG_PEER_GRADIENT=1: gradient sums are stored into the owner's arena
+  int exchange_chunks = 0;  // WG_EXCHANGE_CHUNKS=k: chunks of a pipelined NCCL exchange (0: automatic)
+  int sync_free       = 1;  // WG_SYNC_FREE=0: distributed gathers exchange their counts through the host
+};
+exchange_tuning tuning_from_environment();
+
+}  // namespace wgb
+
 struct wholegraph_comm_ {
   int world_rank = 0;
   int world_size = 1;
@@ -25,6 +42,9 @@ struct wholegraph_comm_ {
   std::set<wholegraph_handle_*> handles;  // freed when the communicator is destroyed
   int next_handle_id = 0;
   uint64_t tag       = 0;  // identical on all ranks; names the side-band unix sockets
+  wgb::exchange_tuning tuning;
+  // Read the tuning variables again and check that all ranks agree (collective, blocking).
+  void reload_tuning();
 
   // Staging for host-side collectives (1 MiB per rank).
   cudaStream_t side_stream = nullptr;

@@ -410,9 +410,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   // WG_GRADIENT_PRESUM=0 routes every gradient row, as the reference does.  By default each rank
   // first adds up its own duplicates, so that an id crosses the wire at most once per rank and a
   // hot row does not flood its owner; the owner then adds the per-rank sums in rank order.
-  const char* presum_env = getenv("WG_GRADIENT_PRESUM");
-  const bool presum = (presum_env == nullptr || presum_env[0] != '0') &&
-                      reduce_duplicates_supported(n, first_row[W], W);
+  const bool presum = comm->tuning.gradient_presum && reduce_duplicates_supported(n, first_row[W], W);
   if (presum) {
     int64_t* cdev = static_cast<int64_t*>(counts_buf.device(3 * W, WHOLEGRAPH_DT_INT64));
     int64_t* uids = static_cast<int64_t*>(uid_buf.device(std::max<int64_t>(n, 1), WHOLEGRAPH_DT_INT64));
@@ -427,8 +425,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     // peer-mapped arena - straight into their owner's region (summation and transfer in one
     // kernel).  At 8 GPUs the fused kernel's remote stores ran no faster than the NCCL exchange
     // (2.74 against 2.63 ms per step), so it is not the default.
-    const char* peer_env = getenv("WG_PEER_GRADIENT");
-    const bool peer      = peer_env != nullptr && peer_env[0] == '1' &&
+    const bool peer = comm->tuning.peer_gradient &&
                       ensure_peer_arena(comm, static_cast<size_t>(plan.max_total_recv()) * row_b, stream);
     std::vector<float*> dest(W);
     char* sums = nullptr;
@@ -451,7 +448,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     } else {
       auto nothing = [](const list_segments&) {};  // rows are already where the exchange reads them
       pipelined_exchange(comm, plan.send_counts, plan.send_displs, plan.recv_counts, plan.recv_displs, sums, recv,
-                         row_b, stream, nothing, nothing, 1);
+                         row_b, stream, nothing, nothing, plan.chunk_count(row_b, 1, comm->tuning.exchange_chunks));
     }
   } else {
     // Every gradient row goes to the owner of its id: the pipeline of a distributed scatter, with
@@ -478,7 +475,8 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
         ps.segments = seg, ps.count = seg.total();
         launch_row_copy(ps, stream);
       },
-      [](const list_segments&) {});  // the update below needs every row: nothing to do per chunk
+      [](const list_segments&) {},  // the update below needs every row: nothing to do per chunk
+      plan.chunk_count(row_b, 0, comm->tuning.exchange_chunks));
   }
   if (plan.total_recv == 0) {
     if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));

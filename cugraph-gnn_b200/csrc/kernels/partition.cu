@@ -42,8 +42,8 @@ __device__ __forceinline__ int owner_of(int64_t id, const int64_t* first_row, in
   if (id < 0 || id >= first_row[world]) return world;
   int r = static_cast<int>(id / per_rank_estimate);
   if (r > world - 1) r = world - 1;
-  while (first_row[r] > id) r--;
-  while (first_row[r + 1] <= id) r++;
+  while (r > 0 && first_row[r] > id) r--;
+  while (r + 1 < world && first_row[r + 1] <= id) r++;
   return r;
 }
 
@@ -226,6 +226,7 @@ void partition_by_owner_builtin_scratch(const void* ids, bool ids_are_64, int64_
 {
   WGB_EXPECTS(world >= 1 && world <= kMaxPartitionRanks, "world size %d exceeds %d", world,
               kMaxPartitionRanks);
+  check_owner_table(first_row, world);
   const size_t need = partition_workspace_bytes(n, world);
   if (need > kBuiltinScratchBytes) {
     throw invalid_input(WHOLEGRAPH_INVALID_VALUE,
@@ -237,6 +238,17 @@ void partition_by_owner_builtin_scratch(const void* ids, bool ids_are_64, int64_
   // be cleared between calls.
   partition_by_owner(ids, ids_are_64, n, first_row, world, builtin_scratch_of_current_device(),
                      sorted_ids, positions, counts, starts, stream);
+}
+
+void check_owner_table(const int64_t* first_row, int world)
+{
+  // The kernels walk the table from an estimate towards the owner; a table that does not start
+  // at row 0 or is out of order would send that walk outside it.
+  bool ok = first_row[0] == 0;
+  for (int r = 0; ok && r < world; r++) ok = first_row[r] <= first_row[r + 1];
+  if (!ok)
+    throw invalid_input(WHOLEGRAPH_INVALID_VALUE,
+                        "first_row must start at 0 and must not decrease from one rank to the next");
 }
 
 size_t partition_workspace_bytes(int64_t n, int world)
@@ -252,6 +264,7 @@ void partition_by_owner(const void* ids, bool ids_are_64, int64_t n, const int64
   WGB_EXPECTS(world >= 1 && world <= kMaxPartitionRanks, "world size %d exceeds %d", world,
               kMaxPartitionRanks);
   WGB_EXPECTS(n < (int64_t(1) << 31), "request list of %ld ids is too long", (long)n);
+  check_owner_table(first_row, world);
   if (n == 0) {
     WGB_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * world, stream));
     WGB_CUDA_CHECK(cudaMemsetAsync(starts, 0, sizeof(int64_t) * world, stream));

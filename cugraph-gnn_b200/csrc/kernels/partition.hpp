@@ -10,6 +10,10 @@ namespace wgb {
 
 constexpr int kMaxPartitionRanks = 64;
 
+// Throws invalid_input(WHOLEGRAPH_INVALID_VALUE) unless first_row[0] == 0 and
+// first_row[r] <= first_row[r + 1] for every rank (HOST array of world + 1 entries).
+void check_owner_table(const int64_t* first_row, int world);
+
 // Bytes of device scratch partition_by_owner needs for a list of n ids.
 size_t partition_workspace_bytes(int64_t n, int world);
 

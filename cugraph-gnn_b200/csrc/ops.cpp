@@ -136,8 +136,7 @@ int64_t exchange_plan::max_total_recv() const
 
 bool ensure_peer_arena(wholegraph_comm_* comm, size_t bytes_per_rank, cudaStream_t stream)
 {
-  const char* e = getenv("WG_PEER_EXCHANGE");
-  if (comm->world_size == 1 || comm->arena_unavailable || (e != nullptr && e[0] == '0')) return false;
+  if (comm->world_size == 1 || comm->arena_unavailable || !comm->tuning.peer_exchange) return false;
   if (comm->arena_idle == nullptr)
     WGB_CUDA_CHECK(cudaEventCreateWithFlags(&comm->arena_idle, cudaEventDisableTiming));
   if (comm->arena != nullptr && comm->arena_bytes >= bytes_per_rank) return true;
@@ -217,14 +216,27 @@ struct phase_timer {
   }
 };
 
-static int exchange_chunk_count(size_t bytes_out, int wanted)
+int exchange_chunk_count(const int64_t* matrix, int world, size_t row_bytes, int wanted, int forced)
 {
-  // WG_EXCHANGE_CHUNKS overrides the number of pipeline chunks (tuning only).
-  const char* e    = getenv("WG_EXCHANGE_CHUNKS");
-  const int forced = e != nullptr ? std::max(1, atoi(e)) : 0;
   if (forced > 0) return std::min(forced, 16);
   if (wanted > 0) return std::min(wanted, 16);
-  return bytes_out < (size_t(16) << 20) ? 1 : 4;
+  // The busiest rank decides for everybody: rows leaving or reaching one rank, its own left out.
+  int64_t busiest = 0;
+  for (int q = 0; q < world; q++) {
+    int64_t out = 0, in = 0;
+    for (int r = 0; r < world; r++) {
+      if (r == q) continue;
+      out += matrix[static_cast<size_t>(q) * world + r];
+      in += matrix[static_cast<size_t>(r) * world + q];
+    }
+    busiest = std::max(busiest, std::max(out, in));
+  }
+  return static_cast<size_t>(busiest) * row_bytes < (size_t(16) << 20) ? 1 : 4;
+}
+
+int exchange_plan::chunk_count(size_t row_bytes, int wanted, int forced) const
+{
+  return exchange_chunk_count(rows.data(), world, row_bytes, wanted, forced);
 }
 
 void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_counts,
@@ -232,13 +244,10 @@ void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_
                         const std::vector<int64_t>& in_displs, char* out_buf, char* in_buf,
                         size_t row_bytes, cudaStream_t stream,
                         const std::function<void(const list_segments&)>& pack,
-                        const std::function<void(const list_segments&)>& unpack, int chunks)
+                        const std::function<void(const list_segments&)>& unpack, int K)
 {
   const int W = comm->world_size, me = comm->world_rank;
-  int64_t total_out = 0;
-  for (int p = 0; p < W; p++)
-    if (p != me) total_out += out_counts[p];
-  const int K     = exchange_chunk_count(static_cast<size_t>(total_out) * row_bytes, chunks);
+  WGB_EXPECTS(K >= 1 && K <= 16, "an exchange runs in 1 to 16 chunks, not %d", K);
   cudaStream_t xs = comm->xchg_stream;
   auto cut        = [K](int64_t c, int k, int64_t* b, int64_t* n) {
     *b = c * k / K;
@@ -380,9 +389,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
   timer.mark("start");
   exchange_plan plan(env);
   // WG_GATHER_DEDUP=0 routes every request, duplicates included, as the reference does.
-  const char* dedup_env   = getenv("WG_GATHER_DEDUP");
-  const bool dedup_wanted = dedup_env == nullptr || dedup_env[0] != '0';
-  const bool dedup = cache == nullptr && dedup_wanted && unique_supported(n, first_row[W]);
+  const bool dedup = cache == nullptr && comm->tuning.gather_dedup && unique_supported(n, first_row[W]);
   plan.build(ids, ids_are_64, n, first_row, comm, stream, dedup);
   timer.mark(dedup ? "unique+counts+ids" : "partition+counts+ids");
 
@@ -429,7 +436,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
           a.segments = seg, a.count = seg.total();
           launch_row_copy(a, stream);
         },
-        [](const list_segments&) {}, 1);
+        [](const list_segments&) {}, plan.chunk_count(row_b, 1, comm->tuning.exchange_chunks));
     }
     timer.mark("exchange");
     row_copy_args expand;  // rows[inverse[i]] -> output row i; ids nobody owns leave their row untouched
@@ -492,7 +499,8 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
       row_copy_args r = reorder;
       r.segments = seg, r.count = seg.total();
       launch_row_copy(r, stream);
-    });
+    },
+    plan.chunk_count(row_b, 0, comm->tuning.exchange_chunks));
   timer.mark("exchange+reorder");
 }
 
@@ -563,7 +571,8 @@ void scatter_distributed(const void* in, const wholegraph_matrix_description_t& 
       row_copy_args a = store;
       a.segments = seg, a.count = seg.total();
       launch_row_copy(a, stream);
-    });
+    },
+    plan.chunk_count(row_b, 0, comm->tuning.exchange_chunks));
   // The reference returns with the local shard updated (scatter_op_impl_nccl.cu:157).
   WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
 }

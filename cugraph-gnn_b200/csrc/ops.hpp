@@ -49,6 +49,9 @@ struct exchange_plan {
   int64_t arrival_start(int q, int r) const;
   int64_t max_total_send() const;
   int64_t max_total_recv() const;
+  // Chunks of a pipelined exchange of rows of `row_bytes` bytes under this plan (see
+  // exchange_chunk_count); the same number on every rank.
+  int chunk_count(size_t row_bytes, int wanted, int forced) const;
   int64_t* sorted_ids = nullptr;  // device, global row ids grouped by owner
   int64_t* positions  = nullptr;  // device, list position of each sorted id
   int64_t* recv_ids   = nullptr;  // device, global row ids this rank must serve
@@ -67,17 +70,23 @@ struct exchange_plan {
 // outgoing rows named by `segments` (array positions in out_buf's row numbering);
 // `unpack(segments)` consumes the incoming rows named by `segments`.  Every chunk is ONE NCCL
 // group over all peers on the communicator's exchange stream.  On return `stream` is ordered
-// after the last unpack.  The self segment (p == rank) is never touched.  `chunks` = 0 picks K
-// (4 above 16 MB of outgoing rows, else 1; WG_EXCHANGE_CHUNKS overrides either way); callers whose
-// pack and unpack do little pass 1, because then there is nothing to overlap and one large
-// exchange is fastest (measured at 8 GPUs: 2.21 ms with K = 1 against 2.29 ms with K = 4).
+// after the last unpack.  The self segment (p == rank) is never touched.  K must be the same on
+// every rank (each chunk is a matched set of sends and receives): take it from
+// exchange_plan::chunk_count.
 struct list_segments;
 void pipelined_exchange(wholegraph_comm_* comm, const std::vector<int64_t>& out_counts,
                         const std::vector<int64_t>& out_displs, const std::vector<int64_t>& in_counts,
                         const std::vector<int64_t>& in_displs, char* out_buf, char* in_buf,
                         size_t row_bytes, cudaStream_t stream,
                         const std::function<void(const list_segments&)>& pack,
-                        const std::function<void(const list_segments&)>& unpack, int chunks = 0);
+                        const std::function<void(const list_segments&)>& unpack, int K);
+
+// Number of chunks K for pipelined_exchange, from data every rank holds identically: the
+// world x world count matrix (matrix[q * world + r] = rows rank q routes to rank r).  `forced` > 0
+// (WG_EXCHANGE_CHUNKS) wins, then `wanted` > 0 (callers whose pack and unpack do little pass 1:
+// with nothing to overlap one large exchange is fastest, measured at 8 GPUs 2.21 ms with K = 1
+// against 2.29 ms with K = 4); otherwise 4 when the busiest rank moves 16 MB or more, else 1.
+int exchange_chunk_count(const int64_t* matrix, int world, size_t row_bytes, int wanted, int forced);
 
 struct cache_view;
 // Gather rows of a DISTRIBUTED table (descriptor `tab` over handle `h`) into `out`.  With

@@ -107,6 +107,57 @@ wholegraph_error_code_t wholegraph_b200_partition_by_owner_no_alloc(const void* 
                                                                       int64_t* starts,
                                                                       void* stream);
 
+/*
+ * De-duplication of a gather's request list, the first step of a DISTRIBUTED gather here (the
+ * reference sorts the whole list and keeps duplicates on the wire,
+ * cpp/src/wholegraph_tensor_ops/functions/exchange_ids_nccl_func.cu:32-104; no C entry point of its
+ * own there).
+ *   ids            n row ids, int32 (ids_are_64 = 0) or int64, device memory
+ *   first_row      HOST array of world + 1 first rows per rank; first_row[0] = 0, not decreasing
+ *   workspace      device scratch of at least wholegraph_b200_unique_workspace_bytes(n, first_row[world])
+ *   unique_ids     out, n int64 (device): the distinct valid ids, ascending, hence grouped by owner;
+ *                  the first sum(counts) entries are written
+ *   inverse        out, n int64 (device): slot in unique_ids of every list position, -1 for ids
+ *                  that are negative or >= first_row[world]
+ *   counts, starts out, world int64 each (device): distinct ids owned by each rank, first slot of its group
+ * n < 2^31 and first_row[world] < 2^32 - 1 (32-bit sort keys), world <= 64; otherwise
+ * WHOLEGRAPH_INVALID_VALUE.  Asynchronous on `stream`.
+ */
+size_t wholegraph_b200_unique_workspace_bytes(int64_t n, int64_t total_rows);
+wholegraph_error_code_t wholegraph_b200_unique_by_owner(const void* ids,
+                                                          int ids_are_64,
+                                                          int64_t n,
+                                                          const int64_t* first_row,
+                                                          int world,
+                                                          void* workspace,
+                                                          size_t workspace_bytes,
+                                                          int64_t* unique_ids,
+                                                          int64_t* inverse,
+                                                          int64_t* counts,
+                                                          int64_t* starts,
+                                                          void* stream);
+
+/*
+ * Number of chunks a pipelined NCCL row exchange runs in (no counterpart in the reference, whose
+ * exchange is one alltoallv, exchange_embeddings_nccl_func.cu:23-64).  Every chunk is a matched set
+ * of sends and receives, so all ranks must arrive at the same number: it is a function of the
+ * world x world count matrix only (matrix[q * world + r] = rows rank q routes to rank r, HOST
+ * memory), which every rank holds after the counts exchange.  forced > 0 wins, then wanted > 0
+ * (both capped at 16); otherwise 4 when the busiest rank sends or receives 16 MiB or more, else 1.
+ */
+int wholegraph_b200_exchange_chunk_count(const int64_t* matrix, int world, size_t row_bytes, int wanted,
+                                         int forced);
+
+/*
+ * Read the WG_* tuning variables of the distributed ops again (WG_PEER_EXCHANGE, WG_GATHER_DEDUP,
+ * WG_GRADIENT_PRESUM, WG_PEER_GRADIENT, WG_EXCHANGE_CHUNKS, WG_SYNC_FREE).  They are read when a
+ * communicator is created; a process that changes them afterwards calls this on every rank
+ * (collective, blocking).  WHOLEGRAPH_LOGIC_ERROR when the ranks do not agree, the check the
+ * reference applies to the parameters of its collective calls
+ * (cpp/src/wholegraph/communicator.hpp:220-249).
+ */
+wholegraph_error_code_t wholegraph_b200_reload_tuning(wholegraph_comm_t comm);
+
 /* The arrays of a cached embedding, for inspection and tests (no counterpart in the reference's
  * C API; its cache object keeps them private, cpp/src/wholegraph/embedding_cache.hpp:64-74):
  * tags and LFU words as int16 [sets, 32] tensors, the cache lines as a [sets * 32, padded dim]

@@ -6,12 +6,16 @@
 // Included from the reference (paths relative to its cpp/src):
 //   wholegraph_tensor_ops/functions/gather_scatter_func.cuh   gather_temp_func / scatter_temp_func
 //   wholegraph_tensor_ops/functions/embedding_optimizer_func.cu  the four optimizer step kernels
+//   wholegraph_tensor_ops/functions/exchange_embeddings_nccl_func.cu  dedup_indice_and_gradients
+//   wholegraph_tensor_ops/thrust_allocator.cpp                 the allocator that function uses
 // The wrappers below only pick template arguments and launch.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "wholegraph_tensor_ops/functions/gather_scatter_func.cuh"
 #include "wholegraph_tensor_ops/functions/embedding_optimizer_func.cu"
+#include "wholegraph_tensor_ops/functions/exchange_embeddings_nccl_func.cu"
+#include "wholegraph_tensor_ops/thrust_allocator.cpp"
 
 using namespace wholegraph_tensor_ops;
 
@@ -152,10 +156,33 @@ extern "C" int wgref_optimizer_step(int opt, const int64_t* ids, const float* gr
   return -2;
 }
 
+// The reference's duplicate-gradient reduction (sort by id, unique, one block per distinct id adding
+// its rows one after the other): int64 ids, fp32 gradients [n, stride].  dedup_grads must hold
+// n * stride floats (the reference strides its output like its input).  `env` is a
+// wholegraph_env_func_t* whose temporary allocator serves the scratch.  Returns the number of
+// distinct ids; the call synchronises the stream (thrust::unique_by_key returns to the host).
+extern "C" long wgref_dedup_gradients(const int64_t* ids, int64_t n, const float* grads, int64_t dim,
+                                      int64_t stride, int64_t* dedup_ids, float* dedup_grads, void* env,
+                                      void* stream)
+{
+  wholegraph_array_description_t id;
+  id.size = n, id.storage_offset = 0, id.dtype = WHOLEGRAPH_DT_INT64;
+  auto gd = mat(n, dim, stride, 0, WHOLEGRAPH_DT_FLOAT);
+  return dedup_indice_and_gradients(ids, id, grads, gd, dedup_ids, dedup_grads,
+                                    static_cast<wholegraph_env_func_t*>(env), static_cast<cudaStream_t>(stream));
+}
+
 // The reference's launch wrappers (compiled above but never called here) name two tensor
 // accessors of its runtime; give the loader something to bind them to.
 extern "C" void* wholegraph_tensor_get_data_pointer(wholegraph_tensor_t) { abort(); }
 extern "C" wholegraph_tensor_description_t* wholegraph_tensor_get_tensor_description(wholegraph_tensor_t)
 {
   abort();
+}
+// Likewise for the row exchange that shares a file with the reduction: never called here.
+extern "C" wholegraph_error_code_t wholegraph_communicator_get_size(int*, wholegraph_comm_t) { abort(); }
+void wholegraph_comm_::alltoallv(const void*, void*, const size_t*, const size_t*, const size_t*, const size_t*,
+                                 wholegraph_dtype_t, cudaStream_t) const
+{
+  ::abort();
 }

@@ -109,3 +109,56 @@ def test_sampling_entry_points_refuse(wgb):
         assert hasattr(lib, name)
     lib.generate_random_positive_int_cpu.argtypes = [C.c_int64, C.c_int64, C.c_void_p]
     assert lib.generate_random_positive_int_cpu(1, 0, None) == int(wgb.ErrorCode.NOT_IMPLEMENTED)
+
+
+def _chunk_count(wgb, matrix, row_bytes, wanted=0, forced=0):
+    m = np.ascontiguousarray(matrix, dtype=np.int64)
+    return wgb.lib().wholegraph_b200_exchange_chunk_count(
+        m.ctypes.data_as(C.POINTER(C.c_int64)), m.shape[0], row_bytes, wanted, forced)
+
+
+def test_exchange_chunk_count_depends_only_on_the_count_matrix(wgb):
+    """Every chunk of a pipelined exchange is a matched set of NCCL sends and receives, so all ranks
+    must pick the same number of chunks.  The choice is a function of the world x world count
+    matrix alone: an asymmetric exchange with ranks on either side of the 16 MiB threshold still
+    gives one answer, the busiest rank's."""
+    row_bytes, threshold_rows = 256, (16 << 20) // 256
+    # rank 0 sends far more than the threshold, the others far less: one K for everybody
+    m = np.array([[5, threshold_rows * 3, 10], [7, 0, 3], [1, 2, 9]])
+    assert _chunk_count(wgb, m, row_bytes) == 4
+    assert _chunk_count(wgb, m.T, row_bytes) == 4                 # the receive side counts as well
+    # just below / just at the threshold on the busiest rank; the diagonal (own rows) never counts
+    below = np.array([[10 ** 9, threshold_rows - 1], [0, 10 ** 9]])
+    assert _chunk_count(wgb, below, row_bytes) == 1
+    at = np.array([[0, threshold_rows], [0, 0]])
+    assert _chunk_count(wgb, at, row_bytes) == 4
+    # a caller's wish and the environment override, both capped
+    assert _chunk_count(wgb, m, row_bytes, wanted=1) == 1
+    assert _chunk_count(wgb, m, row_bytes, wanted=1, forced=8) == 8
+    assert _chunk_count(wgb, m, row_bytes, wanted=99) == 16
+    # what the old rule did wrong: a per-rank answer.  Rank by rank, the outgoing bytes differ ...
+    out_bytes = [(m[q].sum() - m[q, q]) * row_bytes for q in range(3)]
+    assert out_bytes[0] >= 16 << 20 > out_bytes[1]
+    # ... yet the matrix every rank holds gives the same K whichever rank evaluates it.
+    assert len({_chunk_count(wgb, m.copy(), row_bytes) for _ in range(3)}) == 1
+
+
+def test_partition_entry_points_reject_a_bad_owner_table(wgb):
+    """first_row must start at 0 and must not decrease: the kernels walk it from an estimate and
+    would leave the table otherwise.  Both entry points refuse before anything is launched (the
+    pointers below are never dereferenced)."""
+    lib, E = wgb.lib(), wgb.ErrorCode
+    fake = C.c_void_p(0x10000)
+    for table in ([5, 10, 20], [0, 12, 8], [0, 10, 5, 20]):
+        world = len(table) - 1
+        fr = (C.c_int64 * len(table))(*table)
+        rc = lib.wholegraph_b200_partition_by_owner(fake, 1, 100, fr, world, fake, 1 << 20, fake, fake, fake, fake, None)
+        assert rc == int(E.INVALID_VALUE), table
+        rc = lib.wholegraph_b200_partition_by_owner_no_alloc(fake, 1, 100, fr, world, fake, fake, fake, fake, None)
+        assert rc == int(E.INVALID_VALUE), table
+        rc = lib.wholegraph_b200_unique_by_owner(fake, 1, 100, fr, world, fake, 1 << 30, fake, fake, fake, fake, None)
+        assert rc == int(E.INVALID_VALUE), table
+    ok = (C.c_int64 * 3)(0, 10, 20)
+    assert lib.wholegraph_b200_partition_by_owner(fake, 1, 100, ok, 2, fake, 0, fake, fake, fake, fake, None) == int(E.INVALID_VALUE)  # workspace too small
+    assert lib.wholegraph_b200_unique_by_owner(fake, 1, 100, ok, 2, fake, 0, fake, fake, fake, fake, None) == int(E.INVALID_VALUE)
+    assert lib.wholegraph_b200_unique_by_owner(None, 1, 100, ok, 2, fake, 1 << 30, fake, fake, fake, fake, None) == int(E.INVALID_INPUT)

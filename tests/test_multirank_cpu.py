@@ -80,6 +80,103 @@ def test_distributed_gather_protocol_on_gloo(tmp_path, world):
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
 
 
+def _chunked_worker(rank, world, port, rows, dim, ns, result_dir):
+    """The chunked row exchange of a distributed scatter with a different request length on every
+    rank: K comes from the library's rule on the all-gathered count matrix, every chunk is one
+    matched round of sends and receives cut by the rule rows [c*k/K, c*(k+1)/K)."""
+    import ctypes as C
+    sys.path.insert(0, ROOT)
+    from oracle import oracle as orc
+    from __graft_entry__ import load_package
+    wgb = load_package().binding
+    wgb.load_library()
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n = ns[rank]
+        off = orc.equal_partition_offsets(rows, world)
+        req = np.random.default_rng(200 + rank).permutation(rows)[:n].astype(np.int64)   # unique ids
+        rows_in = np.random.default_rng(300 + rank).integers(0, 1 << 15, size=(n, dim)).astype(np.int16)
+        counts, sorted_ids, raw_pos = orc.bucket_sort_ids(req, off)
+        gathered = [torch.zeros(world, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(counts.copy()))
+        matrix = np.stack([g.numpy() for g in gathered])                                  # same on every rank
+        row_bytes = dim * 2
+        m = np.ascontiguousarray(matrix)
+        K = wgb.lib().wholegraph_b200_exchange_chunk_count(m.ctypes.data_as(C.POINTER(C.c_int64)), world, row_bytes, 0, 0)
+        ks = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(ks, torch.tensor([K], dtype=torch.int64))
+        assert len({int(k) for k in ks}) == 1, "ranks disagree on the number of chunks"
+        # the per-rank rule this replaces gives different answers for this matrix
+        own_rule = 1 if (counts.sum() - counts[rank]) * row_bytes < (16 << 20) else 4
+        rules = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(rules, torch.tensor([own_rule], dtype=torch.int64))
+        assert len({int(k) for k in rules}) > 1, "the case does not straddle the threshold"
+
+        send_displs = np.concatenate([[0], np.cumsum(counts)[:-1]])
+        recv_counts = matrix[:, rank]
+        recv_displs = np.concatenate([[0], np.cumsum(recv_counts)[:-1]])
+        packed = rows_in[raw_pos[:int(counts.sum())]]
+        recv_rows = np.zeros((int(recv_counts.sum()), dim), dtype=np.int16)
+        recv_ids = np.zeros(int(recv_counts.sum()), dtype=np.int64)
+        cut = lambda c, k: (c * k // K, c * (k + 1) // K)
+        for k in range(K):
+            ops, bufs = [], []
+            for step in range(1, world):
+                to, frm = (rank + step) % world, (rank - step) % world
+                b, e = cut(int(counts[to]), k)
+                if e > b:
+                    lo = int(send_displs[to])
+                    ops.append(dist.isend(torch.from_numpy(packed[lo + b:lo + e].copy()), to, tag=k))
+                    ops.append(dist.isend(torch.from_numpy(sorted_ids[lo + b:lo + e].copy()), to, tag=100 + k))
+                b, e = cut(int(recv_counts[frm]), k)
+                if e > b:
+                    rbuf = torch.zeros((e - b, dim), dtype=torch.int16)
+                    ibuf = torch.zeros(e - b, dtype=torch.int64)
+                    ops.append(dist.irecv(rbuf, frm, tag=k))
+                    ops.append(dist.irecv(ibuf, frm, tag=100 + k))
+                    bufs.append((int(recv_displs[frm]) + b, rbuf, ibuf))
+            for op in ops:
+                op.wait()
+            for lo, rbuf, ibuf in bufs:
+                recv_rows[lo:lo + rbuf.shape[0]] = rbuf.numpy()
+                recv_ids[lo:lo + rbuf.shape[0]] = ibuf.numpy()
+        lo = int(recv_displs[rank])
+        me = slice(int(send_displs[rank]), int(send_displs[rank] + counts[rank]))
+        recv_rows[lo:lo + int(counts[rank])] = packed[me]
+        recv_ids[lo:lo + int(counts[rank])] = sorted_ids[me]
+        # every row this rank owns that anybody scattered has arrived, with its id
+        all_req = [np.random.default_rng(200 + q).permutation(rows)[:ns[q]].astype(np.int64) for q in range(world)]
+        all_rows = [np.random.default_rng(300 + q).integers(0, 1 << 15, size=(ns[q], dim)).astype(np.int16) for q in range(world)]
+        want = {}
+        for q in range(world):
+            mine = (all_req[q] >= off[rank]) & (all_req[q] < off[rank + 1])
+            for i, r in zip(all_req[q][mine], all_rows[q][mine]):
+                want[(q, int(i))] = r
+        got = 0
+        for q in range(world):
+            seg = slice(int(recv_displs[q]), int(recv_displs[q] + recv_counts[q]))
+            for i, r in zip(recv_ids[seg], recv_rows[seg]):
+                assert np.array_equal(want[(q, int(i))], r)
+                got += 1
+        assert got == len(want)
+        with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:
+            f.write(str(K))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_chunked_exchange_with_unequal_request_lengths_on_gloo(tmp_path):
+    """Rank 0 scatters 40x as many rows as rank 1: rank 0 is above the 16 MiB threshold, rank 1
+    far below it.  With the chunk count taken from the shared count matrix both run 4 matched
+    rounds and every row arrives."""
+    world, dim = 2, 512
+    ns = [40_000, 1_000]           # 40,000 x 1 KiB rows: ~20 MB leave rank 0, ~0.5 MB leave rank 1
+    port = 29650 + (os.getpid() % 200)
+    mp.spawn(_chunked_worker, args=(world, port, 50_021, dim, ns, str(tmp_path)), nprocs=world, join=True)
+    assert [(tmp_path / f"ok{r}").read_text() for r in range(world)] == ["4", "4"]
+
+
 def test_bench_request_lists_are_seeded_and_in_range():
     """The benchmark's bounded power-law ranks: deterministic per seed, inside the table, skewed."""
     sys.path.insert(0, ROOT)
