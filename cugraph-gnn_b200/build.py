@@ -80,11 +80,31 @@ def build(force: bool = False, verbose: bool = False) -> str:
             for fut in [pool.submit(_compile, s, o, verbose) for s, o in jobs]:
                 fut.result()
     if jobs or not os.path.exists(LIB_PATH):
-        cmd = [_nvcc(), "-shared", *ARCH_FLAGS, "-o", LIB_PATH, *objs, "-ldl", "-lpthread", "-lrt"]
-        res = subprocess.run(cmd, capture_output=True, text=True)
-        if res.returncode != 0:
-            raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+        _link(objs, LIB_PATH + ".tmp", [])
+        # Second spelling of the C API: the project this library's interface descends from named
+        # its functions wholememory_*, and binaries built against those names still exist.  Every
+        # exported wholegraph_* function gets a wholememory_* twin at the same address.
+        aliases = [f"--defsym=wholememory_{name[len('wholegraph_'):]}={name}" for name in _exported(LIB_PATH + ".tmp")
+                   if name.startswith("wholegraph_") and not name.startswith("wholegraph_b200_")]
+        os.unlink(LIB_PATH + ".tmp")
+        _link(objs, LIB_PATH, aliases)
     return LIB_PATH
+
+
+def _link(objs: list[str], out: str, linker_flags: list[str]) -> None:
+    cmd = [_nvcc(), "-shared", *ARCH_FLAGS, "-o", out, *objs, "-ldl", "-lpthread", "-lrt"]
+    for flag in linker_flags:
+        cmd += ["-Xlinker", flag]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+
+
+def _exported(lib: str) -> list[str]:
+    """Names of the functions a shared object defines and exports."""
+    res = subprocess.run(["nm", "-D", "--defined-only", lib], capture_output=True, text=True, check=True)
+    return [parts[2] for parts in (line.split() for line in res.stdout.splitlines())
+            if len(parts) == 3 and parts[1] == "T"]
 
 
 if __name__ == "__main__":

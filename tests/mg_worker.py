@@ -24,9 +24,9 @@ def table_values(rows, dim, np_dtype):
 
 def main():
     rank, world, rdv = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
-    scenario = sys.argv[4]
+    scenarios = sys.argv[4].split(",")
     import faulthandler
-    faulthandler.dump_traceback_later(int(os.environ.get("WG_TEST_STACK_AFTER", "90")), exit=True)
+    faulthandler.dump_traceback_later(int(os.environ.get("WG_TEST_STACK_AFTER", "90")) * len(scenarios), exit=True)
     import torch
     from __graft_entry__ import load_package
     pkg = load_package()
@@ -80,6 +80,8 @@ def main():
         return t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy()
 
     def check_gather(mem_type, rows, dim, tdt, odt, n, partition=None, idx_dtype=torch.int64, seed=0):
+        if isinstance(n, (list, tuple)):       # a different request length on every rank
+            n = n[rank % len(n)]
         print(f"rank {rank}: gather {mem_type.name} rows={rows} dim={dim} {tdt}->{odt} n={n}", flush=True)
         t, full = make_table(mem_type, rows, dim, tdt, partition)
         g = torch.Generator(device="cuda").manual_seed(1000 * seed + rank)
@@ -105,7 +107,8 @@ def main():
         # globally unique ids: rank r takes ids congruent to r modulo world
         rng = np.random.default_rng(7)
         perm = rng.permutation(rows)
-        mine = np.ascontiguousarray(perm[rank::world][:n_per_rank]).astype(np.int64)
+        n_of = (lambda r: n_per_rank[r % len(n_per_rank)]) if isinstance(n_per_rank, (list, tuple)) else (lambda r: n_per_rank)
+        mine = np.ascontiguousarray(perm[rank::world][:n_of(rank)]).astype(np.int64)
         vals = np.random.default_rng(100 + rank).uniform(-1, 1, size=(mine.shape[0], dim)).astype(np.float32)
         d_vals = torch.from_numpy(vals).cuda().to(idt)
         tu.scatter(d_vals, torch.from_numpy(mine).cuda(), t, env)
@@ -115,7 +118,7 @@ def main():
         tab, tab_bf16 = host_table(full, tdt)
         tab = tab.copy()
         for r in range(world):
-            ids_r = np.ascontiguousarray(perm[r::world][:n_per_rank]).astype(np.int64)
+            ids_r = np.ascontiguousarray(perm[r::world][:n_of(r)]).astype(np.int64)
             vals_r = np.random.default_rng(100 + r).uniform(-1, 1, size=(ids_r.shape[0], dim)).astype(np.float32)
             rows_r = to_host(torch.from_numpy(vals_r).to(idt))
             orc.scatter(np.ascontiguousarray(rows_r), ids_r, tab, rows_bf16=(idt == torch.bfloat16), table_bf16=tab_bf16)
@@ -210,7 +213,7 @@ def main():
         if policy is not None:
             wgb.destroy_cache_policy(policy)
 
-    if scenario == "fileio":
+    def run_fileio():
         # Plain layout: record r of the files is table row r.  Round robin: blocks of rr records are
         # dealt to the ranks in turn (reference: file_io.cpp:100-200).  Every rank stores its shard.
         rows, dim, rr = 1000 * world + 37, 12, 5
@@ -248,39 +251,151 @@ def main():
         assert np.array_equal(local[:mine_n].cpu().numpy(), want), f"round-robin load differs on rank {rank}"
         wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
         wgb.destroy_wholegraph_tensor(t)
-        wgb.destroy_communicator(comm)
-        print(f"rank {rank} ok", flush=True)
-        return
-    if scenario == "cache":
+
+    def run_cache():
         OT = wgb.WholeGraphOptimizerType
         rows = 128 * 8 * 5
         check_gradient_apply(MT.MtContinuous, OT.OptLazyAdam, 2, rows, 64, 4_000, 3, cache_type=MT.MtContinuous)
         check_gradient_apply(MT.MtDistributed, OT.OptSgd, 1, rows, 33, 3_000, 3, cache_type=MT.MtDistributed)
         check_gradient_apply(MT.MtChunked, OT.OptAdaGrad, 4, 2 * rows, 100, 3_000, 2, torch.bfloat16,
                              cache_type=MT.MtChunked)
-        wgb.destroy_communicator(comm)
-        print(f"rank {rank} ok", flush=True)
-        return
-    if scenario == "optimizer":
+
+    def run_optimizer():
         OT = wgb.WholeGraphOptimizerType
         check_gradient_apply(MT.MtDistributed, OT.OptLazyAdam, 2, 20_011, 64, 6_000, 3)
         check_gradient_apply(MT.MtContinuous, OT.OptSgd, 1, 5_000, 33, 3_000, 2)
         check_gradient_apply(MT.MtDistributed, OT.OptLazyAdam, 2, 9_000, 32, 4_000, 2, hot=700)
         check_gradient_apply(MT.MtDistributed, OT.OptAdaGrad, 4, 8_000, 100, 3_000, 2, torch.float16)
         check_gradient_apply(MT.MtDistributed, OT.OptRmsProp, 3, 3_000, 256, 9_000, 2, torch.bfloat16)
-        wgb.destroy_communicator(comm)
-        print(f"rank {rank} ok", flush=True)
-        return
-    mem = {"continuous": MT.MtContinuous, "distributed": MT.MtDistributed, "chunked": MT.MtChunked}[scenario]
-    check_gather(mem, 100_003, 128, torch.float16, torch.float16, 50_000, seed=1)
-    check_gather(mem, 100_003, 128, torch.float32, torch.float16, 20_001, seed=2)
-    check_gather(mem, 40_000, 33, torch.float32, torch.bfloat16, 7_777, idx_dtype=torch.int32, seed=3)
-    check_gather(mem, 1_000, 8, torch.int64, torch.int64, 0, seed=4)
-    check_gather(mem, 5 * world + 3, 16, torch.bfloat16, torch.float32, 999, seed=5)
-    part = [1000 + 10 * r for r in range(world)]
-    check_gather(mem, sum(part), 64, torch.float32, torch.float32, 12_345, partition=part, seed=6)
-    check_scatter(mem, 30_011, 128, torch.float32, torch.float16, 4_000)
-    check_scatter(mem, 9_000, 20, torch.bfloat16, torch.float32, 2_000)
+
+    def run_memory_type(mem):
+        check_gather(mem, 100_003, 128, torch.float16, torch.float16, 50_000, seed=1)
+        check_gather(mem, 100_003, 128, torch.float32, torch.float16, 20_001, seed=2)
+        check_gather(mem, 40_000, 33, torch.float32, torch.bfloat16, 7_777, idx_dtype=torch.int32, seed=3)
+        check_gather(mem, 1_000, 8, torch.int64, torch.int64, 0, seed=4)
+        check_gather(mem, 5 * world + 3, 16, torch.bfloat16, torch.float32, 999, seed=5)
+        part = [1000 + 10 * r for r in range(world)]
+        check_gather(mem, sum(part), 64, torch.float32, torch.float32, 12_345, partition=part, seed=6)
+        check_scatter(mem, 30_011, 128, torch.float32, torch.float16, 4_000)
+        check_scatter(mem, 9_000, 20, torch.bfloat16, torch.float32, 2_000)
+
+    def run_unequal():
+        # A different request length on every rank, rank 0 far above and the others far below the
+        # 16 MiB at which a pipelined NCCL exchange is cut into chunks, and one rank with nothing to
+        # ask for: every rank must still issue matching collectives.
+        lengths = [150_000] + [5_000 + 100 * r for r in range(1, world - 1)] + [0]
+        check_gather(MT.MtDistributed, 400_003, 128, torch.float16, torch.float16, lengths, seed=7)
+        check_gather(MT.MtDistributed, 400_003, 64, torch.float32, torch.float32, lengths[::-1], seed=8)
+        check_scatter(MT.MtDistributed, 400_003, 128, torch.float32, torch.float16, [90_000] + [3_000] * (world - 1))
+        check_gather(MT.MtContinuous, 50_000, 32, torch.float32, torch.float32, lengths, seed=9)
+
+    def run_stated_size():
+        # BASELINE configuration C3's table at its stated size: 100,000,000 x 128 fp16, CONTINUOUS /
+        # DEVICE, so that shard boundaries fall inside 2 MiB pages and byte offsets pass 2^32.  The
+        # table holds a closed form of (row, column) evaluated on the GPU; a sample of ids (both
+        # ends of every shard among them) is checked against the same form evaluated on the host.
+        rows, dim, n = 100_000_000, 128, 200_000
+        def form(r, c, xp):
+            return (((r * 131 + c * 7) % 2001 - 1000).astype(xp.float32) / 1000.0) if xp is np else \
+                (((r * 131 + c * 7) % 2001 - 1000).to(torch.float32) / 1000.0)
+        for mem in (MT.MtContinuous, MT.MtChunked):
+            print(f"rank {rank}: stated-size gather {mem.name}", flush=True)
+            t = wgb.create_wholegraph_tensor(wgb.make_description([rows, dim], DT.DtHalf), comm, mem, ML.MlDevice)
+            start, count = wgb.C.c_size_t(), wgb.C.c_size_t()
+            wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_start(wgb.C.byref(start), t), "entry_start")
+            wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_count(wgb.C.byref(count), t), "entry_count")
+            cols = torch.arange(dim, device="cuda", dtype=torch.int64)[None, :]
+            for s0 in range(0, count.value, 2_000_000):
+                m = min(2_000_000, count.value - s0)
+                r = torch.arange(start.value + s0, start.value + s0 + m, device="cuda", dtype=torch.int64)[:, None]
+                tu.write_local_shard(t, form(r, cols, torch).to(torch.float16).contiguous(), s0)
+            torch.cuda.synchronize()
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            off = orc.equal_partition_offsets(rows, world)
+            ids = np.random.default_rng(50 + rank).integers(0, rows, size=n).astype(np.int64)
+            edges = np.concatenate([off[:-1], off[1:] - 1, off[1:-1] - 1, [0, rows - 1]])
+            ids[:len(edges)] = edges
+            out = torch.zeros((n, dim), dtype=torch.float16, device="cuda")
+            tu.gather(t, torch.from_numpy(ids).cuda(), out, env)
+            torch.cuda.synchronize()
+            want = form(ids[:, None], np.arange(dim, dtype=np.int64)[None, :], np).astype(np.float16)
+            assert np.array_equal(out.cpu().numpy().view(np.int16), want.view(np.int16)), \
+                f"stated-size gather {mem.name} differs on rank {rank}"
+            # scatter rows all over the table (ids unique across ranks: congruent to the rank) and read them back
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            mine = (np.random.default_rng(3).permutation(rows // world)[:5_000].astype(np.int64) * world + rank)
+            mine[:2] = [rank, (rows // world - 1) * world + rank]
+            mine = np.unique(mine)
+            vals = np.random.default_rng(60 + rank).uniform(-1, 1, size=(len(mine), dim)).astype(np.float16)
+            d_mine = torch.from_numpy(mine).cuda()
+            tu.scatter(torch.from_numpy(vals).cuda(), d_mine, t, env)
+            torch.cuda.synchronize()
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            back = torch.zeros((len(mine), dim), dtype=torch.float16, device="cuda")
+            tu.gather(t, d_mine, back, env)
+            torch.cuda.synchronize()
+            assert np.array_equal(back.cpu().numpy().view(np.int16), vals.view(np.int16)), \
+                f"stated-size scatter {mem.name} differs on rank {rank}"
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            wgb.destroy_wholegraph_tensor(t)
+
+    def run_roundrobin():
+        # Embedding with round_robin_size != 0 over several ranks: the literal remap of the reference
+        # (map_indices_func.cu:16-34) adds the CALLER's first row, so a gather of id i on rank r
+        # returns row entry_start(r) + rr * (block / world) + i % rr.
+        rr, dim, rows = 8, 16, 8 * world * 20
+        emb = wgb.create_embedding(wgb.make_description([rows, dim], DT.DtFloat), comm, MT.MtDistributed, ML.MlDevice,
+                                   round_robin_size=rr)
+        table = wgb.embedding_tensor(emb)
+        full = table_values(rows, dim, np.float32)
+        off = orc.equal_partition_offsets(rows, world)
+        lo, hi = int(off[rank]), int(off[rank + 1])
+        tu.scatter(torch.from_numpy(full[lo:hi]).cuda(), torch.arange(lo, hi, device="cuda", dtype=torch.int64), table, env)
+        torch.cuda.synchronize()
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        ids = np.random.default_rng(rank).integers(0, rows, size=1_000).astype(np.int64)
+        out = torch.zeros((len(ids), dim), dtype=torch.float32, device="cuda")
+        d_ids = torch.from_numpy(ids).cuda()
+        wi, wo = tu.wrap_torch_tensor(d_ids), tu.wrap_torch_tensor(out)
+        wgb.EmbeddingGatherForward(emb, wi, wo, False, env, tu.current_stream_int())
+        torch.cuda.synchronize()
+        wgb.destroy_wholegraph_tensor(wi)
+        wgb.destroy_wholegraph_tensor(wo)
+        mapped = orc.round_robin_map(ids, rr=rr, world=world, entry_start=lo)
+        assert np.array_equal(out.cpu().numpy(), full[mapped]), f"round-robin gather differs on rank {rank}"
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        wgb.destroy_embedding(emb)
+
+    runners = {
+        "fileio": run_fileio, "cache": run_cache, "optimizer": run_optimizer, "unequal": run_unequal,
+        "stated-size": run_stated_size, "roundrobin": run_roundrobin,
+        "continuous": lambda: run_memory_type(MT.MtContinuous),
+        "distributed": lambda: run_memory_type(MT.MtDistributed),
+        "chunked": lambda: run_memory_type(MT.MtChunked),
+    }
+    # A suffix selects one of the library's tuning switches for that scenario; the variables are
+    # read again by a collective call, so one set of processes can run every variant in turn.
+    switches = {"keepdups": {"WG_GATHER_DEDUP": "0"}, "nopresum": {"WG_GRADIENT_PRESUM": "0"},
+                "peerpush": {"WG_PEER_GRADIENT": "1"}, "nccl": {"WG_PEER_EXCHANGE": "0"},
+                "hostcounts": {"WG_SYNC_FREE": "0"}}
+    inherited = {k: os.environ.get(k) for sw in switches.values() for k in sw}
+    for scenario in scenarios:
+        base, suffix = scenario, ""
+        parts = scenario.rsplit("-", 1)
+        if len(parts) == 2 and parts[1] in switches:
+            base, suffix = parts
+        for k, v in inherited.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+        os.environ.update(switches.get(suffix, {}))
+        wgb.check(wgb.lib().wholegraph_b200_reload_tuning(comm), "reload_tuning")
+        t0 = time.time()
+        runners[base]()
+        torch.cuda.synchronize()
+        wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+        print(f"rank {rank}: scenario {scenario} ok in {time.time() - t0:.1f} s", flush=True)
     wgb.destroy_communicator(comm)
     print(f"rank {rank} ok", flush=True)
 

@@ -234,3 +234,39 @@ def test_config2_cast_gather_properties(gpu, wgb, orc):
     torch.cuda.synchronize()
     assert torch.equal(back, new_rows)  # fp16 -> fp32 -> fp16 is the identity
     wgb.destroy_wholegraph_tensor(wt)
+
+
+def test_wholememory_spelling_gathers_and_scatters(gpu, wgb, orc):
+    """wholememory_gather / wholememory_scatter - the names the C API had before the reference's
+    rename, still used by its torch extension (torch_cpp_ext/torch_utils.cpp:11-181) - are exported
+    and do the same work: fp32 table, fp16 output, then fp16 rows scattered back."""
+    import ctypes as C
+    import torch
+    lib = wgb.lib()
+    for name in ("wholememory_gather", "wholememory_scatter"):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = C.c_int, [C.c_void_p] * 3 + [C.POINTER(wgb.EnvFns), C.c_void_p, C.c_int]
+    rng = np.random.default_rng(21)
+    rows, dim, n = 30_000, 128, 5_000
+    table = rng.uniform(-1, 1, size=(rows, dim)).astype(np.float32)
+    idx = rng.integers(0, rows, size=n).astype(np.int64)
+    idx[::41] = -1
+    d_table, d_idx = torch.from_numpy(table).cuda(), torch.from_numpy(idx).cuda()
+    out = torch.zeros((n, dim), dtype=torch.float16, device="cuda")
+    wt, wi, wo = gpu.wrap_torch_tensor(d_table), gpu.wrap_torch_tensor(d_idx), gpu.wrap_torch_tensor(out)
+    stream = C.c_void_p(gpu.current_stream_int())
+    assert lib.wholememory_gather(wt, wi, wo, wgb.cached_env_fns(), stream, -1) == 0
+    torch.cuda.synchronize()
+    want = orc.gather(table, idx, out_dt=orc.DT_HALF, out=np.zeros((n, dim), dtype=np.float16))
+    assert np.array_equal(out.cpu().numpy().view(np.int16), want.view(np.int16))
+    perm = rng.permutation(rows)[:n].astype(np.int64)
+    rows_in = rng.uniform(-1, 1, size=(n, dim)).astype(np.float16)
+    d_rows, d_perm = torch.from_numpy(rows_in).cuda(), torch.from_numpy(perm).cuda()
+    wr, wp = gpu.wrap_torch_tensor(d_rows), gpu.wrap_torch_tensor(d_perm)
+    assert lib.wholememory_scatter(wr, wp, wt, wgb.cached_env_fns(), stream, -1) == 0
+    torch.cuda.synchronize()
+    want_table = table.copy()
+    orc.scatter(rows_in, perm, want_table)
+    assert np.array_equal(d_table.cpu().numpy(), want_table)
+    for w in (wt, wi, wo, wr, wp):
+        wgb.destroy_wholegraph_tensor(w)

@@ -19,29 +19,38 @@ def _device_count():
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.parametrize("scenario", ["continuous", "distributed", "distributed-keepdups", "chunked", "optimizer", "optimizer-nopresum", "optimizer-peerpush", "cache", "fileio"])
+# A suffix after the last dash selects a tuning switch of the library for that scenario (the
+# worker sets the variable and has the library read it again): -keepdups routes duplicates as
+# the reference does, -hostcounts exchanges the counts of a distributed gather through the host,
+# -nccl moves rows by NCCL instead of peer stores, -nopresum routes every gradient row (one
+# summation chain per id), -peerpush writes gradient sums straight into the owner's arena region.
+SCENARIOS = ["continuous", "distributed", "distributed-keepdups", "distributed-hostcounts", "distributed-nccl", "chunked",
+             "optimizer", "optimizer-nopresum", "optimizer-peerpush", "cache", "fileio", "unequal", "unequal-nccl",
+             "unequal-keepdups", "roundrobin", "stated-size"]
+
+
+@pytest.mark.parametrize("scenario", SCENARIOS + ["all-in-one"])
 def test_multi_gpu_gather_scatter(scenario):
+    """One process per GPU.  `all-in-one` runs every scenario in ONE set of processes (one library
+    load and one communicator for all of them): select it with WG_TEST_ALL_IN_ONE=1, which skips
+    the separate runs; without the variable it is skipped."""
     world = min(_device_count(), int(os.environ.get("WG_TEST_WORLD", "8")))
     if world < 2:
         pytest.skip("needs at least two GPUs")
+    together = os.environ.get("WG_TEST_ALL_IN_ONE") == "1"
+    if (scenario == "all-in-one") != together:
+        pytest.skip("runs with WG_TEST_ALL_IN_ONE=1" if scenario == "all-in-one" else "covered by all-in-one")
+    if scenario == "all-in-one":
+        scenario = ",".join(SCENARIOS)
     with tempfile.TemporaryDirectory() as rdv:
         env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-        if scenario.endswith("-keepdups"):       # the path that routes duplicates, as the reference does
-            env["WG_GATHER_DEDUP"] = "0"
-            scenario = scenario.split("-")[0]
-        if scenario.endswith("-nopresum"):       # every gradient row routed, one summation chain per id
-            env["WG_GRADIENT_PRESUM"] = "0"
-            scenario = scenario.split("-")[0]
-        if scenario.endswith("-peerpush"):       # gradient sums written straight into the owner's arena region
-            env["WG_PEER_GRADIENT"] = "1"
-            scenario = scenario.split("-")[0]
         logs = [open(os.path.join(rdv, f"rank{r}.log"), "w+") for r in range(world)]
         procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "mg_worker.py"), str(r), str(world), rdv, scenario],
                                   env=env, stdout=logs[r], stderr=subprocess.STDOUT, text=True)
                  for r in range(world)]
         # A rank that dies leaves its peers waiting in a collective: watch all of them and
         # stop the others as soon as one fails or the time limit passes.
-        deadline = time.time() + float(os.environ.get("WG_TEST_TIMEOUT", "150"))
+        deadline = time.time() + float(os.environ.get("WG_TEST_TIMEOUT", "150")) * (1 + scenario.count(","))
         while True:
             codes = [p.poll() for p in procs]
             if all(c is not None for c in codes):
@@ -63,7 +72,7 @@ def test_multi_gpu_gather_scatter(scenario):
         if keep:
             os.makedirs(keep, exist_ok=True)
             for r, out in enumerate(outs):
-                with open(os.path.join(keep, f"mg_{scenario}_rank{r}.log"), "w") as f:
+                with open(os.path.join(keep, f"mg_{'all' if ',' in scenario else scenario}_rank{r}.log"), "w") as f:
                     f.write(out)
         for r, (p, out) in enumerate(zip(procs, outs)):
             assert p.returncode == 0, f"rank {r} failed (exit {p.returncode}):\n{out[-3000:]}"

@@ -177,3 +177,55 @@ def test_optimizer_parameter_names(gpu, wgb):
     assert wgb.lib().wholegraph_optimizer_set_parameter(o, b"weight_decay", C.byref(v)) == 0
     assert wgb.lib().wholegraph_optimizer_set_parameter(o, b"beta1", C.byref(v)) == int(wgb.ErrorCode.INVALID_INPUT)
     wgb.lib().wholegraph_destroy_embedding_optimizer(o)
+
+
+@pytest.mark.parametrize("rr,rows", [(4, 1003), (16, 4096), (7, 50)])
+def test_round_robin_embedding_gather_and_apply(gpu, wgb, orc, comm, rr, rows):
+    """An embedding created with round_robin_size != 0: ids are remapped before every gather and
+    gradient apply (reference: cpp/src/wholegraph_tensor_ops/functions/map_indices_func.cu:16-34,
+    reached from cpp/src/wholegraph/embedding.cpp:1027-1087) and the table is sized so that every rank
+    stores the same number of rows (embedding.cpp:459-476).  Gather returns the rows the oracle's
+    literal restatement of the remap names; one SGD step lands on those rows and no others."""
+    import torch
+    DT, MT, ML = wgb.WholeGraphDataType, wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation
+    dim, world = 24, 1
+    env = wgb.cached_env_fns()
+    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT.DtFloat), comm, MT.MtContinuous, ML.MlDevice,
+                               round_robin_size=rr)
+    table = wgb.embedding_tensor(emb)
+    extra = min(rows % (world * rr), rr)
+    stored = (rows // (world * rr) * rr + extra) * world
+    got_rows = wgb.lib().wholegraph_tensor_get_tensor_description(table).contents.sizes[0]
+    assert got_rows == stored
+    rng = np.random.default_rng(rr)
+    init = rng.uniform(-1, 1, size=(stored, dim)).astype(np.float32)
+    gpu.scatter(torch.from_numpy(init).cuda(), torch.arange(stored, device="cuda", dtype=torch.int64), table)
+    for idx_dtype in (np.int64, np.int32):
+        ids = rng.integers(0, stored, size=777).astype(idx_dtype)
+        mapped = orc.round_robin_map(ids, rr=rr, world=world, entry_start=0)
+        d_ids = torch.from_numpy(ids).cuda()
+        out = torch.zeros((len(ids), dim), dtype=torch.float32, device="cuda")
+        wi, wo = gpu.wrap_torch_tensor(d_ids), gpu.wrap_torch_tensor(out)
+        wgb.EmbeddingGatherForward(emb, wi, wo, False, env, gpu.current_stream_int())
+        torch.cuda.synchronize()
+        wgb.destroy_wholegraph_tensor(wi)
+        wgb.destroy_wholegraph_tensor(wo)
+        assert np.array_equal(out.cpu().numpy(), init[mapped])
+    # one SGD step through the remap
+    opt = wgb.create_optimizer(wgb.WholeGraphOptimizerType.OptSgd)
+    wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
+    ids = rng.integers(0, stored, size=500).astype(np.int64)
+    grads = rng.uniform(-1, 1, size=(len(ids), dim)).astype(np.float32)
+    d_ids, d_grads = torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda()
+    wi, wg = gpu.wrap_torch_tensor(d_ids), gpu.wrap_torch_tensor(d_grads)
+    wgb.EmbeddingGatherGradientApply(emb, wi, wg, False, 0.1, env, gpu.current_stream_int())
+    torch.cuda.synchronize()
+    wgb.destroy_wholegraph_tensor(wi)
+    wgb.destroy_wholegraph_tensor(wg)
+    want = init.copy()
+    uniq, sums = orc.dedup_gradients(orc.round_robin_map(ids, rr=rr, world=world, entry_start=0), grads)
+    orc.optimizer_apply(1, uniq, sums, want, lr=0.1)
+    got = _read_all(gpu, torch, table, stored, dim, torch.float32).cpu().numpy()
+    assert np.array_equal(got, want)
+    wgb.destroy_embedding(emb)
+    wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
