@@ -60,7 +60,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="auto",
-                    choices=["auto", "c2", "c3", "c3-unique", "c4", "c5", "cache", "unique"])
+                    choices=["auto", "c2", "c3", "c3-unique", "c4", "c5", "cache", "unique", "p2p"])
     ap.add_argument("--rows", type=int, default=0, help="override the table rows (profiling on a small case)")
     ap.add_argument("--ids", type=int, default=0, help="override the ids per rank")
     ap.add_argument("--env-sweep", default="",
@@ -1146,6 +1146,46 @@ def run_append_unique(ctx, steps, warmup):
     return line
 
 
+def run_peer_copy(ctx, steps, warmup):
+    """The NVLink denominator: every rank copies 1 GiB of its right-hand neighbour's shard of a
+    CONTINUOUS/DEVICE allocation (one mapped range, peer pages behind it) into local memory with a
+    plain asynchronous memcpy, all ranks at once; GB/s per direction per GPU."""
+    torch, wgb = ctx.torch, ctx.wgb
+    import ctypes as C
+    world, rank = ctx.world, ctx.rank
+    per_rank = 1 << 30
+    desc = wgb.make_description([world * (per_rank // 256), 256], wgb.WholeGraphDataType.DtInt8)
+    table = wgb.create_wholegraph_tensor(desc, ctx.comm, wgb.WholeGraphMemoryType.MtContinuous,
+                                         wgb.WholeGraphMemoryLocation.MlDevice)
+    handle = C.c_void_p(wgb.lib().wholegraph_tensor_get_memory_handle(table))
+    base = C.c_void_p()
+    wgb.check(wgb.lib().wholegraph_get_global_pointer(C.byref(base), handle), "global_pointer")
+    local = torch.empty(per_rank, dtype=torch.uint8, device="cuda")
+    peer = (rank + 1) % world
+    src = base.value + peer * per_rank
+    stream = C.c_void_p(ctx.tu.current_stream_int())
+
+    def step(i):
+        wgb.check(wgb.lib().wholegraph_b200_memcpy_async(C.c_void_p(local.data_ptr()), C.c_void_p(src), per_rank, stream),
+                  "memcpy_async")
+
+    ms, _, clocks = ctx.timed(step, steps, warmup)
+    gbs = per_rank / (ms * 1e-3) / 1e9
+    line = {"metric": "peer copy GB/s per direction per GPU", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u8", "data": "synthetic",
+            "config": {"workload": f"peer copy: every one of {world} ranks reads 1 GiB of its neighbour's shard of a "
+                                   f"CONTINUOUS/DEVICE allocation into local memory (cudaMemcpyAsync), all at once; "
+                                   f"time = max over ranks"},
+            "gpu_launches": 0, "clocks": clocks,
+            "roofline": {"bound": "nvlink", "achieved": gbs, "peak": NVLINK_NOMINAL_GBS, "unit": "GB/s",
+                         "frac": gbs / NVLINK_NOMINAL_GBS, "traffic": None,
+                         "note": "against the nominal 900 GB/s per direction per GPU"}}
+    ctx.barrier()
+    wgb.destroy_wholegraph_tensor(table)
+    return line
+
+
 def compact(res, keys=("metric", "value", "unit", "ms_per_step", "steps", "gpu_launches", "clocks", "roofline", "parity",
                        "config", "ref_gpu_kernel", "d2h_floor")):
     """The fields of a configuration's line that go into `extra`."""
@@ -1192,7 +1232,11 @@ def main():
     ctx.sweep_workload = workload
 
     line = None
-    if workload in ("cache", "unique"):
+    if workload == "p2p":
+        if not multi:
+            raise SystemExit("the p2p workload needs more than one GPU")
+        line = run_peer_copy(ctx, args.steps, args.warmup)
+    elif workload in ("cache", "unique"):
         if multi:
             raise SystemExit(f"the {workload} workload runs on one GPU")
         line = run_cached_gather(ctx, args.steps, args.warmup) if workload == "cache" else \

@@ -1,7 +1,13 @@
 #include "comm.hpp"
 
 #include <dlfcn.h>
+#include <fcntl.h>
 #include <nccl.h>
+#include <sys/mman.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <thread>
 
 #include <algorithm>
 #include <cstdlib>
@@ -90,6 +96,74 @@ uint64_t fnv1a(const void* p, size_t n, uint64_t h = 1469598103934665603ull)
   return h;
 }
 
+}  // namespace
+}  // namespace wgb
+
+// One cache line per rank and parity: a sequence number and the posted values.  A rank posting
+// call k + 2 overwrites its slot of call k only after it has read everybody's call k + 1, which
+// they post after reading call k: two slots per rank are enough.
+struct wholegraph_comm_::host_board {
+  struct alignas(128) slot {
+    uint64_t seq;
+    int64_t values[wholegraph_comm_::kBoardValues];
+  };
+  slot* slots     = nullptr;  // [2][world]
+  size_t bytes    = 0;
+  uint64_t next   = 1;
+};
+
+namespace wgb {
+namespace {
+
+void setup_board(wholegraph_comm_* c)
+{
+  if (c->world_size == 1) return;
+  using board_t      = wholegraph_comm_::host_board;
+  const size_t bytes = sizeof(board_t::slot) * 2 * static_cast<size_t>(c->world_size);
+  const std::string name = format_string("/wgb_board_%016llx", static_cast<unsigned long long>(c->tag));
+  void* map = MAP_FAILED;
+  int fd    = -1;
+  if (c->world_rank == 0) {
+    shm_unlink(name.c_str());
+    fd = shm_open(name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd >= 0 && ftruncate(fd, static_cast<off_t>(bytes)) != 0) {
+      close(fd);
+      fd = -1;
+    }
+  }
+  c->barrier();  // the segment exists (or rank 0 failed to create it)
+  if (c->world_rank != 0) fd = shm_open(name.c_str(), O_RDWR, 0600);
+  if (fd >= 0) {
+    map = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    close(fd);
+  }
+  int ok = map != MAP_FAILED ? 1 : 0;
+  std::vector<int> all(c->world_size, 0);
+  c->host_allgather(&ok, all.data(), sizeof(int));
+  for (int v : all) ok &= v;
+  if (c->world_rank == 0) shm_unlink(name.c_str());  // the mappings keep it alive
+  if (!ok) {
+    if (map != MAP_FAILED) munmap(map, bytes);
+    WGB_INFO("no shared host memory between the ranks of this communicator: distributed ops exchange sizes "
+             "through the stream");
+    return;
+  }
+  auto* b  = new board_t();
+  b->slots = static_cast<board_t::slot*>(map);
+  b->bytes = bytes;
+  c->board = b;
+  // rank 0 created the segment zero-filled; nobody posts before everybody is here
+  c->barrier();
+}
+
+void destroy_board(wholegraph_comm_* c)
+{
+  if (c->board == nullptr) return;
+  munmap(c->board->slots, c->board->bytes);
+  delete c->board;
+  c->board = nullptr;
+}
+
 void setup_staging(wholegraph_comm_* c)
 {
   WGB_CUDA_CHECK(cudaGetDevice(&c->dev_id));
@@ -152,6 +226,7 @@ wholegraph_comm_* create_comm(const wholegraph_unique_id_t& id, int rank, int si
   }
   setup_staging(c.get());
   c->reload_tuning();
+  setup_board(c.get());
   wholegraph_comm_* raw = c.release();
   {
     std::lock_guard<std::mutex> lk(g_comm_mu);
@@ -193,6 +268,7 @@ wholegraph_comm_* split_comm(wholegraph_comm_* comm, int color, int key)
   }
   setup_staging(c.get());
   c->reload_tuning();
+  setup_board(c.get());
   wholegraph_comm_* raw = c.release();
   {
     std::lock_guard<std::mutex> lk(g_comm_mu);
@@ -217,7 +293,10 @@ void destroy_comm(wholegraph_comm_* comm)
   std::sort(left.begin(), left.end(),
             [](wholegraph_handle_* a, wholegraph_handle_* b) { return a->id < b->id; });
   for (auto* h : left) destroy_handle(h);
+  destroy_board(comm);
   if (comm->barrier_word) cudaFree(comm->barrier_word);
+  if (comm->status_word) cudaFree(comm->status_word);
+  if (comm->status_host) cudaFreeHost(comm->status_host);
   if (comm->arena_idle) cudaEventDestroy(comm->arena_idle);
   if (comm->dev_stage) cudaFree(comm->dev_stage);
   if (comm->pin_stage) cudaFreeHost(comm->pin_stage);
@@ -262,6 +341,32 @@ void wholegraph_comm_::reload_tuning()
       "the WG_* tuning variables differ between the ranks of a communicator; they select which "
       "collectives an op issues and must be equal everywhere");
   tuning = mine;
+}
+
+void wholegraph_comm_::board_exchange(const int64_t* mine, int64_t* all)
+{
+  if (world_size == 1) {
+    memcpy(all, mine, sizeof(int64_t) * kBoardValues);
+    return;
+  }
+  WGB_EXPECTS(board != nullptr, "this communicator has no shared host board");
+  const uint64_t seq      = board->next++;
+  host_board::slot* mine_ = board->slots + (seq & 1) * world_size + world_rank;
+  memcpy(mine_->values, mine, sizeof(int64_t) * kBoardValues);
+  __atomic_store_n(&mine_->seq, seq, __ATOMIC_RELEASE);
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(60);
+  for (int r = 0; r < world_size; r++) {
+    host_board::slot* s = board->slots + (seq & 1) * world_size + r;
+    unsigned spins      = 0;
+    while (__atomic_load_n(&s->seq, __ATOMIC_ACQUIRE) < seq) {
+      if (++spins < 2000) continue;
+      if ((spins & 1023) == 0 && std::chrono::steady_clock::now() > deadline)
+        throw wgb::comm_error(wgb::format_string("rank %d did not reach collective call %llu within 60 s", r,
+                                                 static_cast<unsigned long long>(seq)));
+      std::this_thread::yield();
+    }
+    memcpy(all + static_cast<size_t>(r) * kBoardValues, s->values, sizeof(int64_t) * kBoardValues);
+  }
 }
 
 void wholegraph_comm_::check_async_error()

@@ -67,6 +67,20 @@ struct wholegraph_comm_ {
   bool arena_unavailable    = false;
   cudaEvent_t arena_idle    = nullptr;  // this rank's last read of its own region
   int* barrier_word         = nullptr;  // device word of stream_barrier
+  int* status_word          = nullptr;  // device word a kernel sets when it refuses peer-provided sizes or ids
+  int* status_host          = nullptr;  // pinned copy of status_word, refreshed after every call that uses it
+
+  // Host-to-host board in POSIX shared memory (ranks of one node only): every rank posts a few
+  // numbers per collective call and reads everybody's, without touching a CUDA stream, so that
+  // an op can agree on sizes while the GPUs are still busy with earlier work.  Null when the
+  // ranks cannot share memory; callers then fall back to a stream-synchronising exchange.
+  struct host_board;
+  host_board* board = nullptr;
+  static constexpr int kBoardValues = 6;
+  // Post `mine` (kBoardValues numbers) and return every rank's numbers, rank-major, in `all`
+  // (world_size * kBoardValues).  Collective: every rank calls it the same number of times, in
+  // the same order.  Blocks the host until all ranks have posted (60 s limit, then comm_error).
+  void board_exchange(const int64_t* mine, int64_t* all);
 
   // ---- host collectives (blocking; caller memory is pageable host memory) ----
   void host_allgather(const void* send, void* recv, size_t bytes_per_rank);

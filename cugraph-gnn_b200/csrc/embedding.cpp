@@ -406,6 +406,8 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   // A call on another stream may still be reading this rank's arena region.
   if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->arena_idle, 0));
   char* recv = nullptr;
+  phase_timer timer(stream);
+  timer.mark("start");
 
   // WG_GRADIENT_PRESUM=0 routes every gradient row, as the reference does.  By default each rank
   // first adds up its own duplicates, so that an id crosses the wire at most once per rank and a
@@ -420,7 +422,9 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     } else {
       WGB_CUDA_CHECK(cudaMemsetAsync(cdev, 0, sizeof(int64_t) * 2 * W, stream));
     }
+    timer.mark("group");
     plan.build_grouped(uids, cdev, comm, stream);
+    timer.mark("counts+ids");
     // The sums go into a dense buffer that NCCL moves, or - with WG_PEER_GRADIENT=1 and the
     // peer-mapped arena - straight into their owner's region (summation and transfer in one
     // kernel).  At 8 GPUs the fused kernel's remote stores ran no faster than the NCCL exchange
@@ -443,6 +447,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
     if (n > 0)
       reduce_duplicates_sum(n, first_row[W], g, gd->strides[0], e->dim, W, plan.send_counts.data(), dest.data(), pws,
                             stream);
+    timer.mark("presum");
     if (peer) {
       comm->stream_barrier(stream);  // every sender's sums have landed
     } else {
@@ -478,6 +483,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
       [](const list_segments&) {},  // the update below needs every row: nothing to do per chunk
       plan.chunk_count(row_b, 0, comm->tuning.exchange_chunks));
   }
+  timer.mark("exchange");
   if (plan.total_recv == 0) {
     if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));
     return;
@@ -487,6 +493,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   adjust(plan.recv_ids, true, plan.total_recv);
   sparse_apply(a, ws.device_bytes(sparse_apply_workspace_bytes(plan.total_recv, wl.rows, e->dim)), stream);
   if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));
+  timer.mark("apply");
 }
 
 // Run `fn(mapped indices)`, remapping the ids first when the embedding is sharded round-robin.

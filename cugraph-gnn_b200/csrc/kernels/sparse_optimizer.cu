@@ -9,7 +9,8 @@
 //                         requests the first gradient row, weights and state together, adds
 //                         further duplicates in arrival order (fp32, 16-byte loads), updates
 //                         and writes back; runs longer than 256 rows are registered only
-//   5. sum_blocks_kernel  long runs: one warp per (block of 256 rows, column group)
+//   5. sum_blocks_kernel  long runs: one warp per (block of 256 rows, column group), handed out by
+//                         a device-side counter to a grid that just fills the GPU
 //   6. apply_long_kernel  long runs: block sums added in order, then the same update
 //
 // The summed gradients never go to memory (the reference writes them to a [unique, dim] fp32
@@ -134,10 +135,13 @@ struct apply_params {
   int owners;
   int32_t owner_first_run[kMaxOwnerRanks + 1];
   float* owner_out[kMaxOwnerRanks];
-  int32_t* long_count;    // number of long runs
-  int32_t* slot_count;    // number of partial-sum slots handed out
-  int32_t* slot_run;      // per slot: long run it belongs to
-  int32_t* slot_block;    // per slot: block number inside the run
+  // Long runs and their slots are handed out by ONE 64-bit counter (long runs in the high word,
+  // slots in the low word), so that a run registered later also has the higher first slot: long_slot
+  // ascends and the run of a slot is found by bisection.
+  unsigned long long* long_pack;
+  int32_t* long_count;    // number of long runs (high word of long_pack)
+  int32_t* slot_count;    // number of partial-sum slots handed out (low word of long_pack)
+  int32_t* unit_cursor;   // next (slot, column group) unit (sum_blocks_kernel)
   float* partial;         // [slots, dim] block sums
   cache_view weight_cache;
   cache_view state_cache;
@@ -302,18 +306,16 @@ __global__ void __launch_bounds__(kThreads, 2) apply_kernel(const apply_params p
         *b           = v;
       }
       if (len > kDedupBlock) {
-        const int blocks  = (len + kDedupBlock - 1) / kDedupBlock;
-        const int li      = atomicAdd(p.long_count, 1);
-        const int slot    = atomicAdd(p.slot_count, blocks);
-        p.long_first[li]  = first;
-        p.long_len[li]    = len;
-        p.long_slot[li]   = slot;
-        p.long_beta[li]   = make_float2(beta1t, beta2t);
-        p.long_run[li]    = static_cast<int32_t>(run);
-        for (int b = 0; b < blocks; b++) {
-          p.slot_run[slot + b]   = li;
-          p.slot_block[slot + b] = b;
-        }
+        const int blocks = (len + kDedupBlock - 1) / kDedupBlock;
+        const unsigned long long old =
+          atomicAdd(p.long_pack, (1ull << 32) | static_cast<unsigned long long>(blocks));
+        const int li     = static_cast<int>(old >> 32);
+        const int slot   = static_cast<int>(old & 0xffffffffull);
+        p.long_first[li] = first;
+        p.long_len[li]   = len;
+        p.long_slot[li]  = slot;
+        p.long_beta[li]  = make_float2(beta1t, beta2t);
+        p.long_run[li]   = static_cast<int32_t>(run);
         pos0 = -1;
       } else if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
         s_beta[t][0] = beta1t, s_beta[t][1] = beta2t;
@@ -392,24 +394,37 @@ constexpr int kBlockFlight = 8;  // gradient rows in flight per lane while a blo
 
 // One warp per (partial-sum slot, group of 32 * VEC columns): block b of a long run, rows
 // [b * kDedupBlock, (b + 1) * kDedupBlock) of the run, added in order.  List positions are read 32
-// at a time, one coalesced load ahead of their use.
+// at a time, one coalesced load ahead of their use.  The units are handed out by a device-side
+// counter to a grid that just fills the GPU (their number is only known on the device, and a
+// fixed split leaves most SMs idle while the last wave runs).  The long run a slot belongs to is
+// found by bisection over the runs' first slots, which ascend.
 template <int VEC>
 __global__ void __launch_bounds__(kThreads, 3) sum_blocks_kernel(const apply_params p)
 {
-  constexpr unsigned kFull  = 0xffffffffu;
-  const int lane            = threadIdx.x & 31;
-  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int groups          = (p.dim + 32 * VEC - 1) / (32 * VEC);
-  const int64_t units       = static_cast<int64_t>(*p.slot_count) * groups;
-  for (int64_t unit = warp_global; unit < units; unit += warp_stride) {
-    const int64_t s     = unit / groups;
-    const int c         = static_cast<int>(unit - s * groups) * 32 * VEC + lane * VEC;
-    const bool on       = c < p.dim;
-    const int li        = p.slot_run[s];
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane           = threadIdx.x & 31;
+  const int groups         = (p.dim + 32 * VEC - 1) / (32 * VEC);
+  const int long_runs      = *p.long_count;
+  const int64_t units      = static_cast<int64_t>(*p.slot_count) * groups;
+  auto next_unit = [&]() -> int64_t {
+    int u = 0;
+    if (lane == 0) u = atomicAdd(p.unit_cursor, 1);
+    return __shfl_sync(kFull, u, 0);
+  };
+  for (int64_t unit = next_unit(); unit < units; unit = next_unit()) {
+    const int s   = static_cast<int>(unit / groups);
+    const int c   = static_cast<int>(unit - static_cast<int64_t>(s) * groups) * 32 * VEC + lane * VEC;
+    const bool on = c < p.dim;
+    int lo = 0, hi = long_runs - 1;  // last long run whose first slot is <= s
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (p.long_slot[mid] <= s) lo = mid;
+      else hi = mid - 1;
+    }
+    const int li        = lo;
     const int64_t begin = p.long_first[li];
     const int64_t end   = begin + p.long_len[li];
-    const int64_t first = begin + static_cast<int64_t>(p.slot_block[s]) * kDedupBlock;
+    const int64_t first = begin + static_cast<int64_t>(s - p.long_slot[li]) * kDedupBlock;
     const int64_t last  = first + kDedupBlock < end ? first + kDedupBlock : end;
     float acc[VEC]      = {};
     int next_pos        = first + lane < last ? p.positions[first + lane] : 0;
@@ -439,29 +454,32 @@ __global__ void __launch_bounds__(kThreads, 3) sum_blocks_kernel(const apply_par
       }
     }
     if (on) {
-      float* out = p.partial + s * p.dim + c;
+      float* out = p.partial + static_cast<int64_t>(s) * p.dim + c;
 #pragma unroll
       for (int e = 0; e < VEC; e++) out[e] = acc[e];
     }
   }
 }
 
-constexpr int kPartialFlight = 16;  // block sums in flight per lane while a long run is finished
+constexpr int kPartialFlight = 32;  // block sums in flight per lane while a long run is finished
 
-// One warp per (long run, group of 32 * VEC columns): adds the run's block sums in block order and
-// applies the optimizer to its columns.
-template <int OPT, typename W, int VEC>
+// One warp per (long run, group of 32 columns): adds the run's block sums in block order and
+// applies the optimizer to its columns.  The additions of a column are one chain in block order,
+// so what a warp can do about latency is keep many block sums in flight: one float per lane
+// (a warp reads 128 contiguous bytes of every block sum) and kPartialFlight loads issued before the
+// first addition, which also gives a long run eight warps per 256 columns instead of two.
+template <int OPT, typename W>
 __global__ void __launch_bounds__(kThreads, 2) apply_long_kernel(const apply_params p)
 {
   const int lane            = threadIdx.x & 31;
   const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int groups          = (p.dim + 32 * VEC - 1) / (32 * VEC);
+  const int groups          = (p.dim + 31) / 32;
   const int64_t units       = static_cast<int64_t>(*p.long_count) * groups;
   W* weights                = static_cast<W*>(p.weights);
   for (int64_t unit = warp_global; unit < units; unit += warp_stride) {
     const int64_t li   = unit / groups;
-    const int c        = static_cast<int>(unit - li * groups) * 32 * VEC + lane * VEC;
+    const int c        = static_cast<int>(unit - li * groups) * 32 + lane;
     const bool on      = c < p.dim;
     const uint32_t row = p.keys[p.long_first[li]];
     const int blocks   = (p.long_len[li] + kDedupBlock - 1) / kDedupBlock;
@@ -473,28 +491,19 @@ __global__ void __launch_bounds__(kThreads, 2) apply_long_kernel(const apply_par
     w_row        = reinterpret_cast<W*>(current_copy(p.weight_cache, row, lane, reinterpret_cast<char*>(w_row)));
     if (s_row != nullptr)
       s_row = reinterpret_cast<float*>(current_copy(p.state_cache, row, lane, reinterpret_cast<char*>(s_row)));
-    row_columns<OPT, W, VEC> x;
+    row_columns<OPT, W, 1> x;
     x.load(p, w_row, s_row, c, on);
-    float acc[VEC] = {};
+    float acc[1] = {0.f};
     if (on) {
-#pragma unroll
-      for (int e = 0; e < VEC; e++) acc[e] = part[e];
+      acc[0] = part[0];
       for (int b = 1; b < blocks; b += kPartialFlight) {
-        float v[kPartialFlight][VEC];
+        float v[kPartialFlight];
 #pragma unroll
-        for (int u = 0; u < kPartialFlight; u++) {
-          if (b + u < blocks) {
+        for (int u = 0; u < kPartialFlight; u++)
+          if (b + u < blocks) v[u] = part[static_cast<int64_t>(b + u) * p.dim];
 #pragma unroll
-            for (int e = 0; e < VEC; e++) v[u][e] = part[static_cast<int64_t>(b + u) * p.dim + e];
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < kPartialFlight; u++) {
-          if (b + u < blocks) {
-#pragma unroll
-            for (int e = 0; e < VEC; e++) acc[e] = __fadd_rn(acc[e], v[u][e]);
-          }
-        }
+        for (int u = 0; u < kPartialFlight; u++)
+          if (b + u < blocks) acc[0] = __fadd_rn(acc[0], v[u]);
       }
     }
     x.update_and_store(p, w_row, s_row, c, on, acc, beta.x, beta.y);
@@ -519,7 +528,7 @@ __global__ void round_robin_kernel(const I* ids, I* out, int64_t n, int world, i
 
 struct workspace_layout {
   size_t keys_in, keys_out, pos_in, pos_out, heads, counters, cub, total;
-  size_t long_first, long_len, long_slot, long_beta, long_run, slot_run, slot_block, partial;
+  size_t long_first, long_len, long_slot, long_beta, long_run, partial;
   size_t cub_bytes, select_bytes;
 };
 
@@ -541,7 +550,7 @@ workspace_layout layout_for(int64_t n, int64_t local_rows, int64_t dim)
   l.pos_in         = off, off += align(cnt * 4);
   l.pos_out        = off, off += align(cnt * 4);
   l.heads          = off, off += align(cnt * 4);
-  l.counters       = off, off += 256;  // head count, long-run count, slot count
+  l.counters       = off, off += 256;  // head count, long-run and slot counter, work cursors
   // At most n / block runs are long, and they need at most n / block + (their number) slots.
   const size_t max_long  = cnt / kDedupBlock + 1;
   const size_t max_slots = 2 * max_long;
@@ -550,8 +559,6 @@ workspace_layout layout_for(int64_t n, int64_t local_rows, int64_t dim)
   l.long_slot  = off, off += align(max_long * 4);
   l.long_beta  = off, off += align(max_long * 8);
   l.long_run   = off, off += align(max_long * 4);
-  l.slot_run   = off, off += align(max_slots * 4);
-  l.slot_block = off, off += align(max_slots * 4);
   l.partial    = off, off += align(max_slots * static_cast<size_t>(std::max<int64_t>(dim, 1)) * 4);
   l.cub_bytes      = 0;
   cub::DeviceRadixSort::SortPairs(nullptr, l.cub_bytes, static_cast<const uint32_t*>(nullptr),
@@ -567,20 +574,33 @@ workspace_layout layout_for(int64_t n, int64_t local_rows, int64_t dim)
   return l;
 }
 
+int sm_count()
+{
+  static int n = [] {
+    int dev = 0, count = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev);
+    return count;
+  }();
+  return n;
+}
+
 template <int OPT, typename W>
 void launch_apply(const apply_params& p, bool vec4, int ctas, cudaStream_t stream)
 {
-  // Long runs are rare and their number is only known on the device: fixed modest grids.
-  const int long_ctas = 148 * 4;
+  // The number of long runs and of their blocks is only known on the device: the block sums
+  // take a grid that just fills the GPU and draw their work from a counter; the few long runs
+  // themselves take a fixed modest grid.
+  const int sms       = sm_count();
+  const int long_ctas = sms * 4;
   if (vec4) {
     apply_kernel<OPT, W, 4><<<ctas, kThreads, 0, stream>>>(p);
-    sum_blocks_kernel<4><<<long_ctas, kThreads, 0, stream>>>(p);
-    apply_long_kernel<OPT, W, 4><<<long_ctas, kThreads, 0, stream>>>(p);
+    sum_blocks_kernel<4><<<sms * 3, kThreads, 0, stream>>>(p);
   } else {
     apply_kernel<OPT, W, 1><<<ctas, kThreads, 0, stream>>>(p);
-    sum_blocks_kernel<1><<<long_ctas, kThreads, 0, stream>>>(p);
-    apply_long_kernel<OPT, W, 1><<<long_ctas, kThreads, 0, stream>>>(p);
+    sum_blocks_kernel<1><<<sms * 3, kThreads, 0, stream>>>(p);
   }
+  apply_long_kernel<OPT, W><<<long_ctas, kThreads, 0, stream>>>(p);
 }
 
 template <typename W>
@@ -640,14 +660,16 @@ void bind_workspace(int64_t count, int64_t key_rows, const workspace_layout& l, 
   p->heads       = reinterpret_cast<int32_t*>(ws + l.heads);
   p->head_count = counters, p->n = count;
   p->sentinel   = static_cast<uint32_t>(key_rows);
-  p->long_count = counters + 1, p->slot_count = counters + 2;
+  // counters: [0] run heads, [2..3] the 64-bit long-run / slot counter (slots in the low word),
+  // [4] block-sum cursor
+  p->long_pack   = reinterpret_cast<unsigned long long*>(counters + 2);
+  p->slot_count  = counters + 2, p->long_count = counters + 3;
+  p->unit_cursor = counters + 4;
   p->long_first = reinterpret_cast<int32_t*>(ws + l.long_first);
   p->long_len   = reinterpret_cast<int32_t*>(ws + l.long_len);
   p->long_slot  = reinterpret_cast<int32_t*>(ws + l.long_slot);
   p->long_beta  = reinterpret_cast<float2*>(ws + l.long_beta);
   p->long_run   = reinterpret_cast<int32_t*>(ws + l.long_run);
-  p->slot_run   = reinterpret_cast<int32_t*>(ws + l.slot_run);
-  p->slot_block = reinterpret_cast<int32_t*>(ws + l.slot_block);
   p->partial    = reinterpret_cast<float*>(ws + l.partial);
   p->owners     = 0;
 }
@@ -667,7 +689,7 @@ void group_rows(const void* ids, bool ids_are_64, int64_t count, int64_t key_sta
   size_t cub_bytes = l.cub_bytes;
   WGB_CUDA_CHECK(cub::DeviceRadixSort::SortPairs(ws + l.cub, cub_bytes, keys_in, keys_out, pos_in, pos_out,
                                                  static_cast<int>(count), 0, key_bits(key_rows), stream));
-  WGB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 3 * sizeof(int32_t), stream));
+  WGB_CUDA_CHECK(cudaMemsetAsync(counters, 0, 8 * sizeof(int32_t), stream));
   size_t select_bytes = l.cub_bytes;
   WGB_CUDA_CHECK(cub::DeviceSelect::If(ws + l.cub, select_bytes, thrust::counting_iterator<int>(0), heads, counters,
                                        static_cast<int>(count), is_run_head{keys_out}, stream));
@@ -676,16 +698,12 @@ void group_rows(const void* ids, bool ids_are_64, int64_t count, int64_t key_sta
 
 int apply_grid(int64_t count)
 {
-  static int sm_count = [] {
-    int dev = 0, n = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n;
-  }();
-  // One CTA per tile of kTileRuns distinct rows, grid-stride; the number of rows is only known
-  // on the device, so the grid covers the case that every gradient row has its own id.
+  // One CTA per tile of kTileRuns distinct rows (the hardware hands a new CTA to an SM as soon
+  // as one finishes, so tiles of uneven weight balance themselves), grid-stride beyond a few
+  // waves.  The number of rows is only known on the device, so the grid covers the case that
+  // every gradient row has its own id; CTAs without a tile leave at once.
   const int64_t tiles = (count + kTileRuns - 1) / kTileRuns;
-  return static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(sm_count) * 2 * 8));
+  return static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(sm_count()) * 2 * 8));
 }
 
 struct owner_table {

@@ -24,6 +24,7 @@
 #include "kernels/cache.hpp"
 #include "kernels/partition.hpp"
 #include "kernels/row_copy.hpp"
+#include "kernels/serve_rows.hpp"
 #include "kernels/unique_ids.hpp"
 #include "tensor.hpp"
 
@@ -180,42 +181,6 @@ char* peer_arena_region(wholegraph_comm_* comm, int rank)
   return static_cast<char*>(comm->arena->global_base) + comm->arena->part_offsets[rank];
 }
 
-// WG_TIMING=1: distributed gathers record CUDA events at their phase boundaries and print the
-// phase durations (this synchronises the stream; diagnosis only).
-struct phase_timer {
-  bool on;
-  cudaStream_t stream;
-  std::vector<std::pair<const char*, cudaEvent_t>> marks;
-  explicit phase_timer(cudaStream_t s) : stream(s)
-  {
-    const char* e = getenv("WG_TIMING");
-    on            = e != nullptr && e[0] == '1';
-  }
-  void mark(const char* name)
-  {
-    if (!on) return;
-    cudaEvent_t e;
-    cudaEventCreate(&e);
-    cudaEventRecord(e, stream);
-    marks.push_back({name, e});
-  }
-  ~phase_timer()
-  {
-    if (!on || marks.empty()) return;
-    cudaStreamSynchronize(stream);
-    std::string line;
-    for (size_t i = 1; i < marks.size(); i++) {
-      float ms = 0.f;
-      cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
-      line += format_string(" %s=%.3f", marks[i].first, ms);
-    }
-    float total = 0.f;
-    cudaEventElapsedTime(&total, marks.front().second, marks.back().second);
-    fprintf(stderr, "[wholegraph timing]%s total=%.3f ms\n", line.c_str(), total);
-    for (auto& m : marks) cudaEventDestroy(m.second);
-  }
-};
-
 int exchange_chunk_count(const int64_t* matrix, int world, size_t row_bytes, int wanted, int forced)
 {
   if (forced > 0) return std::min(forced, 16);
@@ -345,6 +310,142 @@ struct table_side {
 
 }  // namespace
 
+// ---- distributed gather without host-side counts --------------------------------------------
+namespace {
+
+// Layout of a rank's region of the exchange arena during such a gather.
+constexpr size_t kRegionHeaderBytes = 2 * sizeof(int64_t) * kMaxServeRanks;  // counts | starts
+size_t region_ids_offset() { return kRegionHeaderBytes; }
+size_t region_rows_offset(int64_t capacity) { return kRegionHeaderBytes + (static_cast<size_t>(capacity) * 8 + 255) / 256 * 256; }
+size_t region_bytes(int64_t capacity, size_t row_bytes)
+{
+  return region_rows_offset(capacity) + static_cast<size_t>(capacity) * row_bytes;
+}
+
+}  // namespace
+
+// Distinct ids only, and nothing about them ever reaches the host: every rank leaves its distinct
+// ids (grouped by owner) and the W group sizes in its own region of the peer-mapped arena; after a
+// barrier in stream order every owner reads, for each requester, "how many ids do you ask of me
+// and where do they start" from that requester's region and stores the rows into the same
+// region (one kernel: peer loads of ids, local loads of rows, peer stores); after a second barrier
+// the requester expands the rows into its output, casting to the output dtype there.  The hosts
+// agree on the region size through the communicator's shared-memory board (request lengths are
+// host data), which synchronises hosts with hosts but no host with a GPU.  Returns false when
+// this path does not apply (no board, no arena, tuning), before anything was enqueued and on
+// every rank alike.
+static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph_matrix_description_t& tab,
+                                         const std::vector<int64_t>& first_row, const void* ids, bool ids_are_64,
+                                         int64_t n, void* out, const wholegraph_matrix_description_t& od,
+                                         wholegraph_env_func_t* env, cudaStream_t stream, int sms)
+{
+  auto* comm          = h->comm;
+  const int W         = comm->world_size;
+  const int me        = comm->world_rank;
+  const size_t es_tab = wholegraph_dtype_get_element_size(tab.dtype);
+  const size_t es_out = wholegraph_dtype_get_element_size(od.dtype);
+  const int64_t dim   = tab.sizes[1];
+  // Rows travel as they are stored; where that would put more bytes on the wire than casting at
+  // the owner (a narrower output dtype), the other path is taken.
+  if (!comm->tuning.sync_free || !comm->tuning.peer_exchange || comm->board == nullptr || comm->arena_unavailable ||
+      W > kMaxServeRanks || es_tab > es_out)
+    return false;
+  const size_t row_b = static_cast<size_t>(dim) * es_tab;
+
+  // Hosts agree on the largest request and check that they are in the same call.
+  int64_t mine[wholegraph_comm_::kBoardValues] = {n, static_cast<int64_t>(row_b), static_cast<int64_t>(h->id),
+                                                  static_cast<int64_t>(tab.dtype) * 16 + static_cast<int64_t>(od.dtype),
+                                                  unique_supported(n, first_row[W]) ? 1 : 0, 0x67617468 /* "gath" */};
+  std::vector<int64_t> all(static_cast<size_t>(W) * wholegraph_comm_::kBoardValues);
+  comm->board_exchange(mine, all.data());
+  int64_t capacity = 1;
+  bool supported   = true;
+  for (int r = 0; r < W; r++) {
+    const int64_t* v = all.data() + static_cast<size_t>(r) * wholegraph_comm_::kBoardValues;
+    WGB_EXPECTS(v[1] == mine[1] && v[2] == mine[2] && v[3] == mine[3] && v[5] == mine[5],
+                "rank %d is in another collective call than rank %d (distributed gather)", r, me);
+    capacity  = std::max(capacity, v[0]);
+    supported = supported && v[4] != 0;
+  }
+  if (!supported) return false;
+  if (!ensure_peer_arena(comm, region_bytes(capacity, row_b), stream)) return false;
+  // The arena is usually larger than asked for: every rank derives the same capacity from its size.
+  {
+    int64_t most = (static_cast<int64_t>(comm->arena_bytes) - static_cast<int64_t>(kRegionHeaderBytes) - 256) /
+                   static_cast<int64_t>(row_b + 8);
+    most = std::min<int64_t>(most, (int64_t(1) << 31) - 2);
+    while (most > capacity && region_bytes(most, row_b) > comm->arena_bytes) most--;
+    capacity = std::max(capacity, most);
+  }
+  if (comm->status_word == nullptr) {
+    WGB_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&comm->status_word), 256));
+    WGB_CUDA_CHECK(cudaMemset(comm->status_word, 0, 256));
+    WGB_CUDA_CHECK(cudaMallocHost(reinterpret_cast<void**>(&comm->status_host), 64));
+    *comm->status_host = 0;
+  }
+  // An earlier call's kernel may have refused a header or an id: the word is copied to the host
+  // after every call and looked at, without waiting, at the next one.
+  if (*comm->status_host != 0) {
+    const int code     = *comm->status_host;
+    *comm->status_host = 0;
+    WGB_CUDA_CHECK(cudaMemsetAsync(comm->status_word, 0, sizeof(int), stream));
+    throw comm_error(format_string("an earlier distributed gather refused %s",
+                                   code == 1 ? "a request header that did not fit its region"
+                                             : "ids outside the shard they were sent to"));
+  }
+
+  phase_timer timer(stream);
+  timer.mark("start");
+  char* my_region     = peer_arena_region(comm, me);
+  int64_t* my_header  = reinterpret_cast<int64_t*>(my_region);
+  int64_t* my_ids     = reinterpret_cast<int64_t*>(my_region + region_ids_offset());
+  char* my_rows       = my_region + region_rows_offset(capacity);
+  temp_buffer workspace(env), inverse_buf(env);
+  int64_t* inverse = static_cast<int64_t*>(inverse_buf.device(std::max<int64_t>(n, 1), WHOLEGRAPH_DT_INT64));
+  void* ws         = workspace.device_bytes(unique_workspace_bytes(n, first_row[W]));
+  unique_by_owner(ids, ids_are_64, n, first_row.data(), W, ws, my_ids, inverse, my_header, my_header + W, stream);
+  timer.mark("unique");
+  comm->stream_barrier(stream);  // every rank's header and ids are in place
+  timer.mark("barrier");
+
+  serve_rows_args s;
+  s.world = W, s.me = me;
+  for (int r = 0; r < W; r++) {
+    char* region       = peer_arena_region(comm, r);
+    s.region[r].header = reinterpret_cast<const int64_t*>(region);
+    s.region[r].ids    = reinterpret_cast<const int64_t*>(region + region_ids_offset());
+    s.region[r].rows   = region + region_rows_offset(capacity);
+  }
+  s.capacity           = capacity;
+  s.first_local_row    = first_row[me];
+  s.local_rows         = first_row[me + 1] - first_row[me];
+  s.shard              = static_cast<const char*>(h->local_ptr) + tab.storage_offset * es_tab;
+  s.shard_stride_bytes = tab.stride * static_cast<int64_t>(es_tab);
+  s.row_bytes          = static_cast<int64_t>(row_b);
+  s.status             = comm->status_word;
+  int64_t bound        = 0;  // a requester asks one owner for at most as many rows as its list is long
+  for (int r = 0; r < W; r++)
+    bound += std::min(all[static_cast<size_t>(r) * wholegraph_comm_::kBoardValues], s.local_rows);
+  s.rows_upper_bound = bound;
+  launch_serve_rows(s, stream);
+  timer.mark("serve");
+  comm->stream_barrier(stream);  // every owner's rows have landed
+  timer.mark("barrier");
+
+  if (n > 0) {
+    row_copy_args expand;  // rows[inverse[i]] -> output row i, cast here; ids nobody owns leave their row untouched
+    expand.src = my_rows, expand.src_dt = tab.dtype, expand.src_stride = dim, expand.src_select = ROW_BY_INDEX;
+    expand.dst = out, expand.dst_dt = od.dtype, expand.dst_stride = od.stride, expand.dst_offset = od.storage_offset;
+    expand.dst_select = ROW_SEQUENTIAL, expand.dim = dim, expand.sm_hint = sms;
+    expand.indices = inverse, expand.indices_are_64 = true, expand.count = n;
+    launch_row_copy(expand, stream);
+  }
+  WGB_CUDA_CHECK(cudaMemcpyAsync(comm->status_host, comm->status_word, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));
+  timer.mark("expand");
+  return true;
+}
+
 // ---- distributed gather ----------------------------------------------------------------------
 void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_description_t& tab,
                         const void* ids, bool ids_are_64, int64_t n, void* out,
@@ -385,6 +486,9 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
 
   // A call on another stream may still be reading this rank's arena region.
   if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->arena_idle, 0));
+  if (cache == nullptr && comm->tuning.gather_dedup &&
+      gather_distributed_sync_free(h, tab, first_row, ids, ids_are_64, n, out, od, env, stream, sms))
+    return;
   phase_timer timer(stream);
   timer.mark("start");
   exchange_plan plan(env);

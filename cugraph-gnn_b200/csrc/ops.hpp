@@ -4,12 +4,17 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <functional>
+#include <string>
+#include <utility>
 #include <vector>
 
 #include <wholegraph/tensor_description.h>
 
 #include "comm.hpp"
+#include "common.hpp"
 #include "env.hpp"
 #include "handle.hpp"
 
@@ -105,6 +110,42 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
 bool ensure_peer_arena(wholegraph_comm_* comm, size_t bytes_per_rank, cudaStream_t stream);
 // Region of `rank` as mapped into this process.
 char* peer_arena_region(wholegraph_comm_* comm, int rank);
+
+// WG_TIMING=1: distributed ops record CUDA events at their phase boundaries and print the phase
+// durations when they return (this synchronises the stream; diagnosis only).
+struct phase_timer {
+  bool on;
+  cudaStream_t stream;
+  std::vector<std::pair<const char*, cudaEvent_t>> marks;
+  explicit phase_timer(cudaStream_t s) : stream(s)
+  {
+    const char* e = getenv("WG_TIMING");
+    on            = e != nullptr && e[0] == '1';
+  }
+  void mark(const char* name)
+  {
+    if (!on) return;
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    cudaEventRecord(e, stream);
+    marks.push_back({name, e});
+  }
+  ~phase_timer()
+  {
+    if (!on || marks.empty()) return;
+    cudaStreamSynchronize(stream);
+    std::string line;
+    for (size_t i = 1; i < marks.size(); i++) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second);
+      line += format_string(" %s=%.3f", marks[i].first, ms);
+    }
+    float total = 0.f;
+    cudaEventElapsedTime(&total, marks.front().second, marks.back().second);
+    fprintf(stderr, "[wholegraph timing]%s total=%.3f ms\n", line.c_str(), total);
+    for (auto& m : marks) cudaEventDestroy(m.second);
+  }
+};
 
 // First row of every rank's shard (world + 1 entries) for rows of `entry_bytes` bytes.
 std::vector<int64_t> entry_offsets_of(wholegraph_handle_* h, size_t entry_bytes);
