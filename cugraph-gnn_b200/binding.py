@@ -96,6 +96,16 @@ class TensorDescription(C.Structure):
     ]
 
 
+class ArrayDescription(C.Structure):
+    """wholegraph_array_description_t"""
+    _fields_ = [("size", C.c_int64), ("storage_offset", C.c_int64), ("dtype", C.c_int)]
+
+
+class MatrixDescription(C.Structure):
+    """wholegraph_matrix_description_t"""
+    _fields_ = [("sizes", C.c_int64 * 2), ("stride", C.c_int64), ("storage_offset", C.c_int64), ("dtype", C.c_int)]
+
+
 class UniqueId(C.Structure):
     _fields_ = [("internal", C.c_char * 128)]
 
@@ -192,6 +202,7 @@ def _declare(lib: C.CDLL) -> None:
                                                       vp, vp, vp, vp, vp]),
         "wholegraph_b200_exchange_chunk_count": (C.c_int, [C.POINTER(i64), C.c_int, sz, C.c_int, C.c_int]),
         "wholegraph_b200_reload_tuning": (C.c_int, [vp]),
+        "wholegraph_b200_gather_from_handle": (C.c_int, [vp, vp, vp, vp, vp, vp, C.POINTER(EnvFns), vp, C.c_int]),
         "wholegraph_b200_version": (C.c_char_p, []),
     }
     optional = {
@@ -210,6 +221,7 @@ def _declare(lib: C.CDLL) -> None:
         "wholegraph_embedding_get_optimizer_state": (vp, [vp, C.c_char_p]),
         "wholegraph_b200_embedding_get_cache_tensors": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
                                                                    C.POINTER(C.c_int)]),
+        "wholegraph_b200_embedding_get_cache_counters": (C.c_int, [vp, C.POINTER(vp), C.POINTER(i64)]),
         "wholegraph_b200_release_output": (C.c_int, [vp]),
         "graph_append_unique": (C.c_int, [vp, vp, vp, vp, C.POINTER(EnvFns), vp]),
         "csr_add_self_loop": (C.c_int, [vp, vp, vp, vp, vp]),

@@ -46,6 +46,11 @@ struct wholegraph_embedding_optimizer_ {
 // they cover, plus this rank's exact access counters.
 struct embedding_cache {
   int coverage               = 32;
+  // A cache on another (smaller) communicator than its table: the ranks of that communicator
+  // cache the WHOLE table between them, read-only; rank r of it holds the sets of table rows
+  // [r * local_rows, (r + 1) * local_rows).
+  bool node_level            = false;
+  int64_t local_rows         = 0;
   wholegraph_tensor_t tags   = nullptr;  // int16 [sets, 32]
   wholegraph_tensor_t lfu    = nullptr;  // int16 [sets, 32]
   wholegraph_tensor_t lines  = nullptr;  // table dtype [sets * 32, padded dim]
@@ -79,6 +84,12 @@ struct wholegraph_embedding_ {
 namespace {
 
 using namespace wgb;
+
+// Turn a failed call into the exception that carries its code to the C boundary.
+void wgb_check(wholegraph_error_code_t rc, const char* what)
+{
+  if (rc != WHOLEGRAPH_SUCCESS) throw invalid_input(rc, format_string("%s failed with code %d", what, (int)rc));
+}
 
 // Row stride padded to 16 bytes (reference: embedding.cpp:32-39).
 int64_t padded_dim_of(int64_t dim, size_t element_size)
@@ -115,6 +126,19 @@ cache_view local_cache_of(const wholegraph_embedding_* e)
 {
   cache_view v;
   if (e == nullptr || !e->cache) return v;
+  if (e->cache->node_level) {
+    // this rank's sets of a cache over the whole table; the table rows have no address here
+    v.tags         = static_cast<uint16_t*>(local_view_of(e->cache->tags).ptr);
+    v.lfu          = static_cast<uint16_t*>(local_view_of(e->cache->lfu).ptr);
+    v.lines        = static_cast<char*>(local_view_of(e->cache->lines).ptr);
+    v.access_count = e->cache->access_count;
+    v.raw_rows     = nullptr;
+    v.first_row    = e->cache->local_rows * e->cache_policy->cache_comm->world_rank;
+    v.rows         = e->cache->local_rows;
+    v.coverage     = e->cache->coverage;
+    v.line_bytes   = e->padded_dim * static_cast<int64_t>(wholegraph_dtype_get_element_size(e->dtype));
+    return v;
+  }
   auto wl        = local_view_of(e->allocated);
   v.tags         = static_cast<uint16_t*>(local_view_of(e->cache->tags).ptr);
   v.lfu          = static_cast<uint16_t*>(local_view_of(e->cache->lfu).ptr);
@@ -154,10 +178,49 @@ cache_view global_cache_of(const wholegraph_embedding_* e)
   return v;
 }
 
+// Cache arrays of a cache on its own communicator (reference: local_cached_global_readonly_embedding,
+// embedding.cpp:761-884, and the cache tensors of embedding_cache.cpp:78-150 created on the cache
+// communicator): sets over all rows of the table, split evenly over the cache communicator's ranks.
+wholegraph_error_code_t create_node_level_cache(wholegraph_embedding_* e)
+{
+  auto* policy = e->cache_policy;
+  std::unique_ptr<embedding_cache> c(new embedding_cache());
+  c->coverage    = coverage_of(policy->cache_ratio);
+  c->node_level  = true;
+  auto* cc       = policy->cache_comm;
+  const int CW   = cc->world_size;
+  const int64_t table_rows = e->allocated->desc.sizes[0];
+  const int64_t sets_total = (table_rows + c->coverage - 1) / c->coverage;
+  const int64_t per_rank   = (sets_total + CW - 1) / CW;
+  c->local_rows            = per_rank * c->coverage;
+  std::vector<size_t> sets_of(CW, static_cast<size_t>(per_rank)), lines_of(CW, static_cast<size_t>(per_rank) * kCacheSetSize);
+  wholegraph_tensor_description_t d;
+  wholegraph_initialize_tensor_desc(&d);
+  d.dim = 2, d.dtype = WHOLEGRAPH_DT_INT16;
+  d.sizes[0] = per_rank * CW, d.sizes[1] = kCacheSetSize, d.strides[0] = kCacheSetSize, d.strides[1] = 1;
+  WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_create_tensor(&c->tags, &d, cc, WHOLEGRAPH_MT_CONTINUOUS, policy->memory_location,
+                                                       sets_of.data()));
+  WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_create_tensor(&c->lfu, &d, cc, WHOLEGRAPH_MT_CONTINUOUS, policy->memory_location,
+                                                       sets_of.data()));
+  d.dtype    = e->dtype;
+  d.sizes[0] = per_rank * CW * kCacheSetSize, d.sizes[1] = e->padded_dim, d.strides[0] = e->padded_dim;
+  WHOLEGRAPH_RETURN_ON_FAIL(wholegraph_create_tensor(&c->lines, &d, cc, WHOLEGRAPH_MT_CONTINUOUS, policy->memory_location,
+                                                       lines_of.data()));
+  WGB_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&c->access_count), c->local_rows * sizeof(int64_t)));
+  WGB_CUDA_CHECK(cudaMemset(c->access_count, 0, c->local_rows * sizeof(int64_t)));
+  WGB_CUDA_CHECK(cudaMemset(local_view_of(c->tags).ptr, 0, per_rank * kCacheSetSize * sizeof(uint16_t)));
+  WGB_CUDA_CHECK(cudaMemset(local_view_of(c->lfu).ptr, 0, per_rank * kCacheSetSize * sizeof(uint16_t)));
+  WGB_CUDA_CHECK(cudaDeviceSynchronize());
+  cc->barrier();
+  e->cache = std::move(c);
+  return WHOLEGRAPH_SUCCESS;
+}
+
 // Cache arrays for a table whose shards are whole sets.
 wholegraph_error_code_t create_cache(wholegraph_embedding_* e)
 {
   auto* policy = e->cache_policy;
+  if (policy->cache_comm != e->comm) return create_node_level_cache(e);
   std::unique_ptr<embedding_cache> c(new embedding_cache());
   c->coverage = coverage_of(policy->cache_ratio);
   const int W = e->comm->world_size;
@@ -199,6 +262,100 @@ wholegraph_error_code_t create_cache(wholegraph_embedding_* e)
   return WHOLEGRAPH_SUCCESS;
 }
 
+// Gather through a read-only cache that lives on a smaller communicator than its table (every
+// node caching the whole table for itself).  Reference: local_cached_global_readonly_embedding::gather,
+// embedding.cpp:772-884, with update_cache_different_comm (embedding_cache_func.cu:511-622) and
+// try_gather_cached_func (gather_cached_func.cu:366-467).
+//   adjust_cache: the ids go to the cache ranks that hold their sets; there the LFU update only
+//   decides which rows get which lines; the rows are then gathered from the table (a collective of
+//   the table's communicator when the table is DISTRIBUTED) and scattered into the lines.
+//   lookup: hits are copied from the lines (every cache rank maps all of them), misses are left to
+//   one gather from the table over the list of missed ids.
+void node_level_cached_gather(wholegraph_embedding_* e, wholegraph_tensor_t indices, wholegraph_tensor_t output,
+                              const void* ids, bool ids_are_64, int64_t n, void* out,
+                              const wholegraph_matrix_description_t& od, const wholegraph_matrix_description_t& tab,
+                              bool adjust_cache, wholegraph_env_func_t* env, cudaStream_t stream)
+{
+  auto* cc      = e->cache_policy->cache_comm;
+  const int CW  = cc->world_size;
+  const size_t es = wholegraph_dtype_get_element_size(e->dtype);
+  cache_view mine = local_cache_of(e);
+  auto table_gather = [&](void* id_ptr, wholegraph_dtype_t id_dt, int64_t count, wholegraph_tensor_t dst) {
+    // collective on the table's communicator when the table is DISTRIBUTED: always called
+    wholegraph_tensor_description_t idd;
+    wholegraph_initialize_tensor_desc(&idd);
+    idd.dim = 1, idd.dtype = id_dt, idd.sizes[0] = count, idd.strides[0] = 1;
+    wholegraph_tensor_t idt = nullptr;
+    wgb_check(wholegraph_make_tensor_from_pointer(&idt, id_ptr, &idd), "make_tensor_from_pointer");
+    auto rc = wholegraph_gather(e->user, idt, dst, env, stream, e->gather_sms);
+    wholegraph_destroy_tensor(idt);
+    wgb_check(rc, "wholegraph_gather");
+  };
+  if (adjust_cache) {
+    std::vector<int64_t> first_row(CW + 1);
+    for (int r = 0; r <= CW; r++) first_row[r] = e->cache->local_rows * r;
+    exchange_plan plan(env);
+    plan.build(ids, ids_are_64, n, first_row, cc, stream);
+    const int64_t m = std::max<int64_t>(plan.total_recv, 1);
+    temp_buffer ws(env), rows_buf(env), lines_buf(env), count_buf(env), fetched(env);
+    auto* load_rows  = static_cast<int64_t*>(rows_buf.device(m, WHOLEGRAPH_DT_INT64));
+    auto* load_lines = static_cast<int64_t*>(lines_buf.device(m, WHOLEGRAPH_DT_INT64));
+    auto* load_count = static_cast<int*>(count_buf.device(64, WHOLEGRAPH_DT_INT));
+    WGB_CUDA_CHECK(cudaMemsetAsync(load_rows, 0xff, sizeof(int64_t) * m, stream));   // -1: skipped by both copies
+    WGB_CUDA_CHECK(cudaMemsetAsync(load_lines, 0xff, sizeof(int64_t) * m, stream));
+    WGB_CUDA_CHECK(cudaMemsetAsync(load_count, 0, sizeof(int), stream));
+    if (plan.total_recv > 0) {
+      cache_view decide  = mine;
+      decide.load_rows   = load_rows;
+      decide.load_lines  = load_lines;
+      decide.load_count  = load_count;
+      cache_update(plan.recv_ids, true, plan.total_recv, decide,
+                   ws.device_bytes(cache_update_workspace_bytes(plan.total_recv)), stream);
+    }
+    // rows to load: table -> dense buffer -> lines (entries left at -1 move nothing)
+    char* rows = static_cast<char*>(fetched.device_bytes(static_cast<size_t>(m) * e->padded_dim * es));
+    wholegraph_tensor_description_t rd;
+    wholegraph_initialize_tensor_desc(&rd);
+    rd.dim = 2, rd.dtype = e->dtype, rd.sizes[0] = m, rd.sizes[1] = e->dim, rd.strides[0] = e->padded_dim, rd.strides[1] = 1;
+    wholegraph_tensor_t rt = nullptr;
+    wgb_check(wholegraph_make_tensor_from_pointer(&rt, rows, &rd), "make_tensor_from_pointer");
+    table_gather(load_rows, WHOLEGRAPH_DT_INT64, m, rt);
+    wholegraph_destroy_tensor(rt);
+    row_copy_args put;
+    put.src = rows, put.src_dt = e->dtype, put.src_stride = e->padded_dim, put.src_select = ROW_SEQUENTIAL;
+    put.dst = mine.lines, put.dst_dt = e->dtype, put.dst_stride = e->padded_dim, put.dst_select = ROW_BY_INDEX;
+    put.dim = e->dim, put.count = m, put.indices = load_lines, put.indices_are_64 = true;
+    launch_row_copy(put, stream);
+    // the other ranks of the cache communicator read these lines next
+    WGB_CUDA_CHECK(cudaStreamSynchronize(stream));
+    cc->barrier();
+  }
+  // lookup in all sets of the cache communicator (tags and lines are mapped on each of its ranks)
+  cache_view all = mine;
+  auto base      = [](wholegraph_tensor_t t) { return wholegraph_tensor_get_memory_handle(t)->global_base; };
+  all.tags       = static_cast<uint16_t*>(base(e->cache->tags));
+  all.lfu        = static_cast<uint16_t*>(base(e->cache->lfu));
+  all.lines      = static_cast<char*>(base(e->cache->lines));
+  all.access_count = nullptr;
+  all.first_row  = 0;
+  all.rows       = e->cache->local_rows * CW;
+  temp_buffer address_buf(env), miss_buf(env);
+  const int64_t cap = std::max<int64_t>(n, 1);
+  auto* addr = static_cast<int64_t*>(address_buf.device(cap, WHOLEGRAPH_DT_INT64));
+  auto* miss = static_cast<int64_t*>(miss_buf.device(cap, WHOLEGRAPH_DT_INT64));
+  if (n > 0) {
+    cache_lookup(ids, ids_are_64, n, all, false, addr, stream, miss);
+    row_copy_args g;
+    g.src_dt = tab.dtype, g.src_stride = tab.stride, g.src_offset = 0;
+    g.src_select = ROW_BY_ADDRESS, g.indices = addr, g.indices_are_64 = true;
+    g.dst = out, g.dst_dt = od.dtype, g.dst_stride = od.stride, g.dst_offset = od.storage_offset;
+    g.dim = e->dim, g.count = n, g.sm_hint = e->gather_sms;
+    launch_row_copy(g, stream);
+  }
+  (void)indices;
+  table_gather(miss, WHOLEGRAPH_DT_INT64, n, output);  // rows the cache left out
+}
+
 // Forward gather through the cache.
 void cached_gather(wholegraph_embedding_* e, wholegraph_tensor_t indices, wholegraph_tensor_t output,
                    bool adjust_cache, wholegraph_env_func_t* env, cudaStream_t stream)
@@ -226,6 +383,10 @@ void cached_gather(wholegraph_embedding_* e, wholegraph_tensor_t indices, wholeg
   wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(e->allocated);
   auto* comm            = e->comm;
   const cache_view mine = local_cache_of(e);
+  if (e->cache->node_level) {
+    node_level_cached_gather(e, indices, output, ids, ids_are_64, n, out, od, tab, adjust_cache, env, stream);
+    return;
+  }
   if (comm->world_size == 1 || !cache_is_mapped(e)) {
     // Owners look their cache up for the ids routed to them and serve the rows.
     gather_distributed(h, tab, ids, ids_are_64, n, out, od, env, stream, e->gather_sms, &mine, adjust_cache);
@@ -622,11 +783,22 @@ wholegraph_error_code_t wholegraph_create_embedding(
     WGB_ERROR("wholegraph_create_embedding: the description must be a 2-D matrix");
     return WHOLEGRAPH_INVALID_INPUT;
   }
+  if (cache_policy != nullptr && cache_policy->cache_comm == nullptr) return WHOLEGRAPH_INVALID_INPUT;
   if (cache_policy != nullptr && cache_policy->cache_comm != comm) {
-    // A cache on a smaller communicator than the table (every node caching the whole table for
-    // itself) is not built.
-    WGB_ERROR("a cache must be on the communicator of its embedding");
-    return WHOLEGRAPH_NOT_IMPLEMENTED;
+    // A cache on its own, smaller communicator: every such group of ranks caches the whole table
+    // for itself, read-only (reference rules: embedding.cpp:972-987).
+    if (cache_policy->cache_comm->world_size > comm->world_size) {
+      WGB_ERROR("the cache communicator must not be larger than the embedding's");
+      return WHOLEGRAPH_INVALID_INPUT;
+    }
+    if (cache_policy->memory_type != WHOLEGRAPH_MT_CONTINUOUS) {
+      WGB_ERROR("For local cached global readonly embedding, cache_memory_type should be continuous.");
+      return WHOLEGRAPH_INVALID_INPUT;
+    }
+    if (cache_policy->access_type != WHOLEGRAPH_AT_READONLY) {
+      WGB_ERROR("Only ReadOnly access type supported for local cached global readonly embedding.");
+      return WHOLEGRAPH_INVALID_INPUT;
+    }
   }
   if (cache_policy != nullptr && cache_policy->memory_location != WHOLEGRAPH_ML_DEVICE) {
     WGB_ERROR("a cache must be in device memory");
@@ -712,6 +884,10 @@ wholegraph_error_code_t wholegraph_embedding_set_optimizer(wholegraph_embedding_
     return WHOLEGRAPH_NOT_SUPPORTED;
   }
   if (optimizer == nullptr) return WHOLEGRAPH_SUCCESS;
+  if (e->cache && e->cache->node_level) {
+    WGB_ERROR("an embedding behind a read-only cache cannot be trained");
+    return WHOLEGRAPH_NOT_SUPPORTED;
+  }
   if (e->dtype != WHOLEGRAPH_DT_FLOAT && e->dtype != WHOLEGRAPH_DT_HALF && e->dtype != WHOLEGRAPH_DT_BF16) {
     WGB_ERROR("Only float, half and bf16 embeddings support training.");
     return WHOLEGRAPH_NOT_IMPLEMENTED;
@@ -790,6 +966,16 @@ wholegraph_error_code_t wholegraph_b200_embedding_get_cache_tensors(wholegraph_e
   if (lfu) *lfu = e->cache->lfu;
   if (lines) *lines = e->cache->lines;
   if (set_coverage) *set_coverage = e->cache->coverage;
+  return WHOLEGRAPH_SUCCESS;
+}
+
+wholegraph_error_code_t wholegraph_b200_embedding_get_cache_counters(wholegraph_embedding_t e,
+                                                                       int64_t** counters,
+                                                                       int64_t* local_rows)
+{
+  if (e == nullptr || !e->cache || counters == nullptr) return WHOLEGRAPH_INVALID_INPUT;
+  *counters = e->cache->access_count;
+  if (local_rows != nullptr) *local_rows = local_cache_of(e).rows;
   return WHOLEGRAPH_SUCCESS;
 }
 

@@ -35,7 +35,7 @@ constexpr int kLookupLanes = 4;
 constexpr int kLookupIds   = 32 / kLookupLanes;
 
 __global__ void __launch_bounds__(kThreads) lookup_kernel(const void* ids, int is64, int64_t n, cache_view c,
-                                                          int mark_modified, int64_t* row_address)
+                                                          int mark_modified, int64_t* row_address, int64_t* miss_ids)
 {
   const int lane            = threadIdx.x & 31;
   const int sub             = lane & (kLookupLanes - 1);  // which quarter of the tag set
@@ -45,7 +45,8 @@ __global__ void __launch_bounds__(kThreads) lookup_kernel(const void* ids, int i
   for (int64_t base = warp_global * kLookupIds; base < n; base += warp_stride * kLookupIds) {
     const int64_t i     = base + slot;
     const bool live     = i < n;
-    const int64_t local = live ? load_id(ids, is64, i) - c.first_row : -1;
+    const int64_t id    = live ? load_id(ids, is64, i) : -1;
+    const int64_t local = live ? id - c.first_row : -1;
     const bool in_range = live && local >= 0 && local < c.rows;
     int64_t set         = 0;
     int hit             = -1;
@@ -63,7 +64,8 @@ __global__ void __launch_bounds__(kThreads) lookup_kernel(const void* ids, int i
     hit = max(hit, __shfl_xor_sync(0xffffffffu, hit, 1));
     hit = max(hit, __shfl_xor_sync(0xffffffffu, hit, 2));
     if (sub != 0 || !live) continue;
-    if (!in_range) {
+    if (miss_ids != nullptr) miss_ids[i] = (in_range && hit >= 0) ? -1 : id;  // negative ids stay skipped
+    if (!in_range || (hit < 0 && c.raw_rows == nullptr)) {
       row_address[i] = -1;
     } else if (hit >= 0) {
       // equal ids in other groups may store the same value at the same time
@@ -209,19 +211,33 @@ __global__ void __launch_bounds__(kThreads)
 
     // 4. move data: evicted modified lines go back to the table, new rows are loaded
     const bool evicted = my_row >= 0 && ((keep >> lane) & 1u) == 0;
-    for (int l = 0; l < 32; l++) {
-      const int ev_row = __shfl_sync(0xffffffffu, (evicted && modified) ? my_row : -1, l);
-      if (ev_row >= 0)
-        copy_line(c.raw_rows + (row0 + ev_row) * c.line_bytes, c.lines + (set * kCacheSetSize + l) * c.line_bytes,
-                  c.line_bytes, lane);
+    if (c.raw_rows == nullptr) {
+      // The table has no address here (and the cache is read-only: no line is modified): list
+      // the rows to load with their lines and let the caller move them.
+      int base = 0;
+      if (lane == 0 && new_m != 0) base = atomicAdd(c.load_count, __popc(new_m));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (is_new) {
+        c.load_rows[base + new_rank]  = c.first_row + row0 + top.row;
+        c.load_lines[base + new_rank] = set * kCacheSetSize + target;
+      }
+    } else {
+      for (int l = 0; l < 32; l++) {
+        const int ev_row = __shfl_sync(0xffffffffu, (evicted && modified) ? my_row : -1, l);
+        if (ev_row >= 0)
+          copy_line(c.raw_rows + (row0 + ev_row) * c.line_bytes, c.lines + (set * kCacheSetSize + l) * c.line_bytes,
+                    c.line_bytes, lane);
+      }
     }
     __syncwarp();
-    for (int l = 0; l < 32; l++) {
-      const int nrow  = __shfl_sync(0xffffffffu, is_new ? top.row : -1, l);
-      const int nslot = __shfl_sync(0xffffffffu, target, l);
-      if (nrow >= 0)
-        copy_line(c.lines + (set * kCacheSetSize + nslot) * c.line_bytes, c.raw_rows + (row0 + nrow) * c.line_bytes,
-                  c.line_bytes, lane);
+    if (c.raw_rows != nullptr) {
+      for (int l = 0; l < 32; l++) {
+        const int nrow  = __shfl_sync(0xffffffffu, is_new ? top.row : -1, l);
+        const int nslot = __shfl_sync(0xffffffffu, target, l);
+        if (nrow >= 0)
+          copy_line(c.lines + (set * kCacheSetSize + nslot) * c.line_bytes, c.raw_rows + (row0 + nrow) * c.line_bytes,
+                    c.line_bytes, lane);
+      }
     }
 
     // 5. new tags and scaled LFU words: lane = line
@@ -326,12 +342,13 @@ void check_view(const cache_view& c)
 }  // namespace
 
 void cache_lookup(const void* ids, bool ids_are_64, int64_t n, const cache_view& c, bool mark_modified,
-                  int64_t* row_address, cudaStream_t stream)
+                  int64_t* row_address, cudaStream_t stream, int64_t* miss_ids)
 {
   if (n == 0) return;
   check_view(c);
+  WGB_EXPECTS(c.raw_rows != nullptr || miss_ids != nullptr, "a cache without table addresses needs a miss list");
   lookup_kernel<<<grid_for((n + kLookupIds - 1) / kLookupIds), kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, c, mark_modified ? 1 : 0,
-                                                      row_address);
+                                                      row_address, miss_ids);
   count_kernel_launch();
   WGB_LAUNCH_CHECK(stream);
 }
@@ -344,6 +361,8 @@ void cache_update(const void* ids, bool ids_are_64, int64_t n, const cache_view&
   if (n == 0) return;
   check_view(c);
   WGB_EXPECTS(n < (int64_t(1) << 31), "access batch of %ld ids is too long", (long)n);
+  WGB_EXPECTS(c.raw_rows != nullptr || (c.load_rows != nullptr && c.load_lines != nullptr && c.load_count != nullptr),
+              "a cache without table addresses needs load lists");
   const layout l  = layout_for(n);
   char* ws        = static_cast<char*>(workspace);
   auto* keys      = reinterpret_cast<uint32_t*>(ws + l.keys);

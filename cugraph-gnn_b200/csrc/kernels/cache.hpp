@@ -33,13 +33,25 @@ struct cache_view {
   int64_t rows          = 0;        // multiple of coverage
   int coverage          = 32;
   int64_t line_bytes    = 0;        // = table row stride in bytes (multiple of 16)
+  // A read-only cache whose table this rank cannot address (raw_rows == nullptr; the table lives
+  // on a larger communicator): an update then only decides which rows get which lines and
+  // appends them to these lists, and the caller moves the rows (a gather from the table, a
+  // scatter into the lines).  Entries beyond *load_count are left as they were (callers fill the
+  // lists with -1, which both copies skip, so the count never has to reach the host).
+  int64_t* load_rows    = nullptr;  // out: global row id of every line to load
+  int64_t* load_lines   = nullptr;  // out: index of that line in `lines`
+  int* load_count       = nullptr;  // in/out: entries used
 };
 
 // row_address[i] = address of the current copy of row ids[i]: its cache line on a hit, the table
 // row otherwise, -1 for ids outside [first_row, first_row + rows).  With mark_modified, hit lines
 // get their modified bit set (the caller is about to write the row).
+// With `miss_ids` (n int64, for caches whose table rows have no address here): on a hit
+// miss_ids[i] = -1 and row_address[i] is the line; on a miss row_address[i] = -1 and miss_ids[i] is
+// the id itself, so that a gather of `miss_ids` from the table fills exactly the rows the cache
+// left out (role of the reference's try_gather_cached_func, gather_cached_func.cu:251-467).
 void cache_lookup(const void* ids, bool ids_are_64, int64_t n, const cache_view& c, bool mark_modified,
-                  int64_t* row_address, cudaStream_t stream);
+                  int64_t* row_address, cudaStream_t stream, int64_t* miss_ids = nullptr);
 
 size_t cache_update_workspace_bytes(int64_t n);
 

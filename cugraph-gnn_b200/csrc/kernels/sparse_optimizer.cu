@@ -247,7 +247,7 @@ struct row_columns {
 };
 
 constexpr int kTileRuns    = kThreads;  // runs whose metadata one CTA stages at a time, one per thread (64-run tiles measured slower: 1.26 against 1.18 ms per C5 step)
-constexpr int kApplyFlight = 4;         // duplicate rows a lane requests (for two column groups) before adding
+constexpr int kApplyFlight = 8;         // duplicate rows a lane requests (for two column groups) before adding
 
 // Distinct rows with at most kDedupBlock duplicates: summed and applied here.  Longer runs are
 // only registered, with one partial-sum slot per block of kDedupBlock rows.

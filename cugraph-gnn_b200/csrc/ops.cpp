@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+#include <wholegraph/wholegraph_b200.h>
 #include <wholegraph/wholegraph_tensor_op.h>
 
 #include "common.hpp"
@@ -743,10 +744,12 @@ wholegraph_error_code_t wholegraph_gather(wholegraph_tensor_t table,
               (long)tab.sizes[1]);
     return WHOLEGRAPH_LOGIC_ERROR;
   }
-  if (idx.size == 0 || tab.sizes[1] == 0) return WHOLEGRAPH_SUCCESS;
-  if (ids == nullptr || out == nullptr) return WHOLEGRAPH_INVALID_INPUT;
-
   wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(table);
+  // A distributed gather is a collective: a rank with nothing to ask for still serves the others.
+  const bool collective = h != nullptr && h->type == WHOLEGRAPH_MT_DISTRIBUTED && h->comm->world_size > 1;
+  if ((idx.size == 0 && !collective) || tab.sizes[1] == 0) return WHOLEGRAPH_SUCCESS;
+  if (idx.size > 0 && (ids == nullptr || out == nullptr)) return WHOLEGRAPH_INVALID_INPUT;
+
   if (h != nullptr && h->type == WHOLEGRAPH_MT_DISTRIBUTED) {
     gather_distributed(h, tab, ids, ids_are_64, idx.size, out, od, p_env_fns, stream, gather_sms);
     return WHOLEGRAPH_SUCCESS;
@@ -769,6 +772,55 @@ wholegraph_error_code_t wholegraph_gather(wholegraph_tensor_t table,
   launch_row_copy(a, stream);
   return WHOLEGRAPH_SUCCESS;
   WGB_API_END("wholegraph_gather")
+}
+
+wholegraph_error_code_t wholegraph_b200_gather_from_handle(wholegraph_handle_t handle,
+                                                             const wholegraph_matrix_description_t* table_desc,
+                                                             const void* indices,
+                                                             const wholegraph_array_description_t* indices_desc,
+                                                             void* output,
+                                                             const wholegraph_matrix_description_t* output_desc,
+                                                             wholegraph_env_func_t* p_env_fns,
+                                                             void* stream_ptr,
+                                                             int gather_sms)
+{
+  if (handle == nullptr || table_desc == nullptr || indices_desc == nullptr || output_desc == nullptr)
+    return WHOLEGRAPH_INVALID_INPUT;
+  WGB_API_BEGIN
+  auto stream = static_cast<cudaStream_t>(stream_ptr);
+  const wholegraph_matrix_description_t& tab = *table_desc;
+  const wholegraph_matrix_description_t& od  = *output_desc;
+  const bool f_ok = wholegraph_dtype_is_floating_number(tab.dtype) && wholegraph_dtype_is_floating_number(od.dtype);
+  const bool i_ok = wholegraph_dtype_is_integer_number(tab.dtype) && wholegraph_dtype_is_integer_number(od.dtype);
+  if (!f_ok && !i_ok) return WHOLEGRAPH_LOGIC_ERROR;
+  if (od.sizes[0] != indices_desc->size || od.sizes[1] != tab.sizes[1]) return WHOLEGRAPH_LOGIC_ERROR;
+  if (indices_desc->dtype != WHOLEGRAPH_DT_INT && indices_desc->dtype != WHOLEGRAPH_DT_INT64) return WHOLEGRAPH_INVALID_INPUT;
+  const bool ids_are_64 = indices_desc->dtype == WHOLEGRAPH_DT_INT64;
+  const int64_t n       = indices_desc->size;
+  const bool collective = handle->type == WHOLEGRAPH_MT_DISTRIBUTED && handle->comm->world_size > 1;
+  if ((n == 0 && !collective) || tab.sizes[1] == 0) return WHOLEGRAPH_SUCCESS;
+  if (n > 0 && (indices == nullptr || output == nullptr)) return WHOLEGRAPH_INVALID_INPUT;
+  const void* ids = indices == nullptr ? nullptr
+                                       : static_cast<const char*>(indices) +
+                                           indices_desc->storage_offset * (ids_are_64 ? 8 : 4);
+  const size_t row_bytes = wholegraph_dtype_get_element_size(tab.dtype) * static_cast<size_t>(tab.stride);
+  if (handle->type == WHOLEGRAPH_MT_DISTRIBUTED) {
+    gather_distributed(handle, tab, ids, ids_are_64, n, output, od, p_env_fns, stream, gather_sms);
+    return WHOLEGRAPH_SUCCESS;
+  }
+  row_copy_args a;
+  a.src_dt = tab.dtype, a.src_stride = tab.stride, a.src_offset = tab.storage_offset;
+  a.src_select = ROW_BY_INDEX;
+  a.dst = output, a.dst_dt = od.dtype, a.dst_stride = od.stride, a.dst_offset = od.storage_offset;
+  a.count = n, a.dim = tab.sizes[1], a.indices = ids, a.indices_are_64 = ids_are_64, a.sm_hint = gather_sms;
+  if (handle->type == WHOLEGRAPH_MT_CHUNKED)
+    fill_chunks(&a.chunks, handle, row_bytes);
+  else
+    a.src = handle->global_base;
+  WGB_EXPECTS(handle->type == WHOLEGRAPH_MT_CHUNKED || a.src != nullptr, "the handle has no mapped range");
+  launch_row_copy(a, stream);
+  return WHOLEGRAPH_SUCCESS;
+  WGB_API_END("wholegraph_b200_gather_from_handle")
 }
 
 wholegraph_error_code_t wholegraph_scatter(wholegraph_tensor_t input_tensor,
@@ -826,10 +878,12 @@ wholegraph_error_code_t wholegraph_scatter(wholegraph_tensor_t input_tensor,
               (long)id_.sizes[1], (long)tab.sizes[1]);
     return WHOLEGRAPH_LOGIC_ERROR;
   }
-  if (idx.size == 0 || tab.sizes[1] == 0) return WHOLEGRAPH_SUCCESS;
-  if (ids == nullptr || in == nullptr) return WHOLEGRAPH_INVALID_INPUT;
-
   wholegraph_handle_* h = wholegraph_tensor_get_memory_handle(table);
+  // A distributed scatter is a collective: a rank with nothing to store still receives rows.
+  const bool collective = h != nullptr && h->type == WHOLEGRAPH_MT_DISTRIBUTED && h->comm->world_size > 1;
+  if ((idx.size == 0 && !collective) || tab.sizes[1] == 0) return WHOLEGRAPH_SUCCESS;
+  if (idx.size > 0 && (ids == nullptr || in == nullptr)) return WHOLEGRAPH_INVALID_INPUT;
+
   if (h != nullptr && h->type == WHOLEGRAPH_MT_DISTRIBUTED) {
     scatter_distributed(in, id_, ids, ids_are_64, idx.size, h, tab, p_env_fns, stream, scatter_sms);
     return WHOLEGRAPH_SUCCESS;

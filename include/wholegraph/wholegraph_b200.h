@@ -158,6 +158,28 @@ int wholegraph_b200_exchange_chunk_count(const int64_t* matrix, int world, size_
  */
 wholegraph_error_code_t wholegraph_b200_reload_tuning(wholegraph_comm_t comm);
 
+/*
+ * wholegraph_gather on a memory handle and raw device pointers instead of tensors: the form in which the
+ * reference's NCCL-mode neighbour sampling calls the distributed gather on the CSR row-pointer and column
+ * handles of a graph (wholegraph_gather_nccl, cpp/src/wholegraph_tensor_ops/gather_op_impl.h:24-32, called
+ * from cpp/src/wholegraph_ops/unweighted_sample_without_replacement_nccl_func.cuh:236 and :364; an internal
+ * C++ symbol there).  Works on CONTINUOUS, CHUNKED and DISTRIBUTED handles.
+ *   table_desc    rows x columns view of the handle's memory (stride and storage offset in elements)
+ *   indices       int32 / int64 row ids, device memory; indices_desc->storage_offset elements are skipped
+ *   output        first element of the output storage; output_desc gives rows (= number of indices),
+ *                 columns (= the table's), row stride and storage offset
+ * Same checks, casts and skipped negative ids as wholegraph_gather.  Collective for a DISTRIBUTED handle.
+ */
+wholegraph_error_code_t wholegraph_b200_gather_from_handle(wholegraph_handle_t handle,
+                                                             const wholegraph_matrix_description_t* table_desc,
+                                                             const void* indices,
+                                                             const wholegraph_array_description_t* indices_desc,
+                                                             void* output,
+                                                             const wholegraph_matrix_description_t* output_desc,
+                                                             wholegraph_env_func_t* p_env_fns,
+                                                             void* stream,
+                                                             int gather_sms);
+
 /* The arrays of a cached embedding, for inspection and tests (no counterpart in the reference's
  * C API; its cache object keeps them private, cpp/src/wholegraph/embedding_cache.hpp:64-74):
  * tags and LFU words as int16 [sets, 32] tensors, the cache lines as a [sets * 32, padded dim]
@@ -169,6 +191,15 @@ wholegraph_error_code_t wholegraph_b200_embedding_get_cache_tensors(wholegraph_e
                                                                       wholegraph_tensor_t* lfu,
                                                                       wholegraph_tensor_t* lines,
                                                                       int* set_coverage);
+
+/* This rank's exact access counters of a cached embedding: one int64 per local row (device memory owned by
+ * the embedding), in local row order.  The replacement rule ranks the rows of a set by these counters; the
+ * reference keeps approximate scaled counters for cached lines instead and exact ones only for the rest
+ * (cpp/src/wholegraph_tensor_ops/functions/embedding_cache_func.cuh:132-141), and exposes neither.  For
+ * inspection and tests.  WHOLEGRAPH_INVALID_INPUT for an embedding without a cache. */
+wholegraph_error_code_t wholegraph_b200_embedding_get_cache_counters(wholegraph_embedding_t embedding,
+                                                                       int64_t** counters,
+                                                                       int64_t* local_rows);
 
 /* Memory context for the output allocator of the two built-in env functions above: an op that
  * produces an output of a size only it knows (graph_append_unique) calls

@@ -79,11 +79,12 @@ def main():
     def to_host(t):
         return t.view(torch.int16).cpu().numpy().view(np.uint16) if t.dtype == torch.bfloat16 else t.cpu().numpy()
 
-    def check_gather(mem_type, rows, dim, tdt, odt, n, partition=None, idx_dtype=torch.int64, seed=0):
+    def check_gather(mem_type, rows, dim, tdt, odt, n, partition=None, idx_dtype=torch.int64, seed=0,
+                     location=ML.MlDevice):
         if isinstance(n, (list, tuple)):       # a different request length on every rank
             n = n[rank % len(n)]
         print(f"rank {rank}: gather {mem_type.name} rows={rows} dim={dim} {tdt}->{odt} n={n}", flush=True)
-        t, full = make_table(mem_type, rows, dim, tdt, partition)
+        t, full = make_table(mem_type, rows, dim, tdt, partition, location)
         g = torch.Generator(device="cuda").manual_seed(1000 * seed + rank)
         idx = torch.randint(0, rows, (n,), generator=g, device="cuda").to(idx_dtype)
         if n > 10:
@@ -101,9 +102,9 @@ def main():
         wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
         wgb.destroy_wholegraph_tensor(t)
 
-    def check_scatter(mem_type, rows, dim, tdt, idt, n_per_rank):
+    def check_scatter(mem_type, rows, dim, tdt, idt, n_per_rank, location=ML.MlDevice):
         print(f"rank {rank}: scatter {mem_type.name} rows={rows} dim={dim} {idt}->{tdt}", flush=True)
-        t, full = make_table(mem_type, rows, dim, tdt)
+        t, full = make_table(mem_type, rows, dim, tdt, None, location)
         # globally unique ids: rank r takes ids congruent to r modulo world
         rng = np.random.default_rng(7)
         perm = rng.permutation(rows)
@@ -132,7 +133,7 @@ def main():
         wgb.destroy_wholegraph_tensor(t)
 
     def check_gradient_apply(mem_type, opt_type, opt_code, rows, dim, n, steps, table_dtype=torch.float32,
-                             cache_type=None, hot=0):
+                             cache_type=None, hot=0, location=ML.MlDevice):
         print(f"rank {rank}: gradient apply {mem_type.name} opt={opt_code} rows={rows} dim={dim} "
               f"cache={cache_type}", flush=True)
         policy = None
@@ -140,7 +141,7 @@ def main():
             policy = wgb.create_cache_policy(comm, cache_type, ML.MlDevice, wgb.WholeGraphAccessType.AtReadWrite,
                                              0.25)
         emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(tu.TORCH_TO_WG[table_dtype])), comm,
-                                   mem_type, ML.MlDevice, cache_policy=policy)
+                                   mem_type, location, cache_policy=policy)
         opt = wgb.create_optimizer(opt_type, weight_decay=0.01)
         wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
         table = wgb.embedding_tensor(emb)
@@ -279,6 +280,70 @@ def main():
         check_scatter(mem, 30_011, 128, torch.float32, torch.float16, 4_000)
         check_scatter(mem, 9_000, 20, torch.bfloat16, torch.float32, 2_000)
 
+    def run_hosttable():
+        # Tables in host memory shared by the ranks: CONTINUOUS / HOST is one POSIX shared-memory
+        # segment registered with CUDA on every rank, DISTRIBUTED / HOST pinned memory per rank
+        # (reference: memory_handle.cpp:503-546); then the reference's primary cached mode, a device
+        # cache in front of a host table (embedding.cpp:567-759), trained through and written back.
+        for mem in (MT.MtContinuous, MT.MtDistributed):
+            check_gather(mem, 60_007, 128, torch.float32, torch.float16, 9_000, seed=11, location=ML.MlHost)
+            check_gather(mem, 10_000, 20, torch.int64, torch.int64, 3_333, idx_dtype=torch.int32, seed=12,
+                         location=ML.MlHost)
+            check_scatter(mem, 20_011, 64, torch.float32, torch.float16, 3_000, location=ML.MlHost)
+        OT = wgb.WholeGraphOptimizerType
+        rows = 128 * world * 6
+        check_gradient_apply(MT.MtContinuous, OT.OptLazyAdam, 2, rows, 64, 4_000, 3, cache_type=MT.MtContinuous,
+                             location=ML.MlHost)
+        check_gradient_apply(MT.MtDistributed, OT.OptSgd, 1, rows, 40, 3_000, 2, cache_type=MT.MtDistributed,
+                             location=ML.MlHost)
+
+    def run_nodecache():
+        # A read-only cache on a smaller communicator than its table: the world is split into two
+        # halves (one "node" each) and every half caches the whole DISTRIBUTED table for itself
+        # (reference: local_cached_global_readonly_embedding, embedding.cpp:761-884).
+        AT = wgb.WholeGraphAccessType
+        half = wgb.C.c_void_p()
+        color = 0 if rank < (world + 1) // 2 else 1
+        wgb.check(wgb.lib().wholegraph_split_communicator(wgb.C.byref(half), comm, color, rank), "split")
+        for mem, tdt, dim in ((MT.MtDistributed, torch.float32, 48), (MT.MtContinuous, torch.float16, 128)):
+            rows = 128 * world * 7 + 5
+            policy = wgb.create_cache_policy(half, MT.MtContinuous, ML.MlDevice, AT.AtReadOnly, 0.25)
+            emb = wgb.create_embedding(wgb.make_description([rows, dim], DT(tu.TORCH_TO_WG[tdt])), comm, mem, ML.MlDevice,
+                                       cache_policy=policy)
+            table = wgb.embedding_tensor(emb)
+            trows = wgb.lib().wholegraph_tensor_get_tensor_description(table).contents.sizes[0]
+            full = table_values(trows, dim, np.float32)
+            start, count = wgb.C.c_size_t(), wgb.C.c_size_t()
+            wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_start(wgb.C.byref(start), table), "entry_start")
+            wgb.check(wgb.lib().wholegraph_tensor_get_local_entry_count(wgb.C.byref(count), table), "entry_count")
+            lo, hi = start.value, start.value + count.value
+            tu.scatter(torch.from_numpy(full[lo:hi]).cuda().to(tdt), torch.arange(lo, hi, device="cuda", dtype=torch.int64),
+                       table, env)
+            torch.cuda.synchronize()
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            want_all = to_host(torch.from_numpy(full).to(tdt))
+            for step in range(5):
+                rng = np.random.default_rng(100 * step + rank)
+                n = 2_000 + 300 * rank
+                ids = np.where(rng.random(n) < 0.8, rng.integers(0, rows // 10, size=n), rng.integers(0, rows, size=n))
+                ids = ids.astype(np.int64)
+                d_ids = torch.from_numpy(ids).cuda()
+                out = torch.zeros((n, dim), dtype=tdt, device="cuda")
+                wi, wo = tu.wrap_torch_tensor(d_ids), tu.wrap_torch_tensor(out)
+                wgb.EmbeddingGatherForward(emb, wi, wo, step != 2, env, tu.current_stream_int())
+                torch.cuda.synchronize()
+                wgb.destroy_wholegraph_tensor(wi)
+                wgb.destroy_wholegraph_tensor(wo)
+                assert np.array_equal(to_host(out), want_all[ids]), f"node-level cached gather {step} differs on rank {rank}"
+                wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            tags = wgb.embedding_cache_tensors(emb)[0]
+            lt = tu.local_shard_as_torch(tags)
+            assert int((lt.view(torch.int16) != 0).sum().item()) > 0, "nothing was cached"
+            wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            wgb.destroy_embedding(emb)
+            wgb.destroy_cache_policy(policy)
+        wgb.destroy_communicator(half)
+
     def run_unequal():
         # A different request length on every rank, rank 0 far above and the others far below the
         # 16 MiB at which a pipelined NCCL exchange is cut into chunks, and one rank with nothing to
@@ -368,7 +433,7 @@ def main():
 
     runners = {
         "fileio": run_fileio, "cache": run_cache, "optimizer": run_optimizer, "unequal": run_unequal,
-        "stated-size": run_stated_size, "roundrobin": run_roundrobin,
+        "stated-size": run_stated_size, "roundrobin": run_roundrobin, "hosttable": run_hosttable, "nodecache": run_nodecache,
         "continuous": lambda: run_memory_type(MT.MtContinuous),
         "distributed": lambda: run_memory_type(MT.MtDistributed),
         "chunked": lambda: run_memory_type(MT.MtChunked),

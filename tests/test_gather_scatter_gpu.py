@@ -270,3 +270,104 @@ def test_wholememory_spelling_gathers_and_scatters(gpu, wgb, orc):
     assert np.array_equal(d_table.cpu().numpy(), want_table)
     for w in (wt, wi, wo, wr, wp):
         wgb.destroy_wholegraph_tensor(w)
+
+
+@pytest.mark.parametrize("mem_name", ["MtContinuous", "MtDistributed"])
+@pytest.mark.parametrize("tab_dt,out_dt", [(1, 2), (2, 2), (6, 6)])
+def test_host_resident_tables(gpu, wgb, orc, mem_name, tab_dt, out_dt):
+    """Tables in pinned host memory (CONTINUOUS / HOST and DISTRIBUTED / HOST handles, reference:
+    cpp/src/wholegraph/memory_handle.cpp:503-546): the same kernels read and write them through
+    their device-visible addresses; results must equal the oracle's, as for device tables
+    (reference grid: wholegraph_gather_tests.cu:271-413 runs every case for HOST as well)."""
+    import torch
+    MT, ML, DT = wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphDataType
+    comm = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+    rng = np.random.default_rng(tab_dt * 10 + out_dt)
+    rows, dim, n = 20_000, 96, 7_000
+    table_np = _random_table(rng, orc, rows, dim, tab_dt)
+    t = wgb.create_wholegraph_tensor(wgb.make_description([rows, dim], DT(tab_dt)), comm, getattr(MT, mem_name), ML.MlHost)
+    gpu.write_local_shard(t, _to_device(torch, table_np, tab_dt).contiguous())
+    idx = rng.integers(0, rows, size=n).astype(np.int64)
+    idx[::53] = -1
+    sentinel = _random_table(rng, orc, n, dim, out_dt)
+    d_out = _to_device(torch, sentinel.copy(), out_dt)
+    gpu.gather(t, torch.from_numpy(idx).cuda(), d_out)
+    torch.cuda.synchronize()
+    want = sentinel.copy()
+    orc.gather(table_np, idx, out_dt=out_dt, out=want, table_bf16=(tab_dt == 4))
+    assert np.array_equal(_to_host(torch, d_out, out_dt).view(want.dtype), want)
+    # scatter back into the host table at unique ids and read it through a gather of all rows
+    perm = rng.permutation(rows)[:n].astype(np.int64)
+    rows_in = _random_table(rng, orc, n, dim, out_dt)
+    gpu.scatter(_to_device(torch, rows_in, out_dt), torch.from_numpy(perm).cuda(), t)
+    back = _to_device(torch, np.zeros_like(table_np), tab_dt)
+    gpu.gather(t, torch.arange(rows, device="cuda", dtype=torch.int64), back)
+    torch.cuda.synchronize()
+    want_table = table_np.copy()
+    orc.scatter(rows_in, perm, want_table, rows_bf16=(out_dt == 4), table_bf16=(tab_dt == 4))
+    assert np.array_equal(_to_host(torch, back, tab_dt).view(want_table.dtype), want_table)
+    wgb.destroy_wholegraph_tensor(t)
+    wgb.destroy_communicator(comm)
+
+
+@pytest.mark.parametrize("mem_name", ["MtContinuous", "MtDistributed", "MtChunked"])
+def test_gather_from_a_handle_with_raw_pointers(gpu, wgb, orc, mem_name):
+    """The form in which NCCL-mode neighbour sampling calls the gather (reference:
+    cpp/src/wholegraph_ops/unweighted_sample_without_replacement_nccl_func.cuh:236, :364): a memory
+    handle, descriptors and raw device pointers; an int64 CSR row-pointer array gathered at
+    [v, v + 1] pairs, then column ids gathered at edge positions (int32 columns, int64 output)."""
+    import ctypes as C
+    import torch
+    MT, ML, DT = wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphDataType
+    lib = wgb.lib()
+    comm = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+    rng = np.random.default_rng(31)
+    nodes, centers = 40_000, 3_000
+    degree = rng.integers(0, 12, size=nodes)
+    row_ptr = np.concatenate([[0], np.cumsum(degree)]).astype(np.int64)
+    col = rng.integers(0, nodes, size=int(row_ptr[-1])).astype(np.int32)
+
+    def handle_with(values, dt):
+        t = wgb.create_wholegraph_tensor(wgb.make_description([len(values)], dt), comm, getattr(MT, mem_name), ML.MlDevice)
+        gpu.write_local_shard(t, torch.from_numpy(values).cuda())
+        return t, C.c_void_p(lib.wholegraph_tensor_get_memory_handle(t))
+
+    t_row, h_row = handle_with(row_ptr, DT.DtInt64)
+    t_col, h_col = handle_with(col, DT.DtInt)
+    env, stream = wgb.cached_env_fns(), C.c_void_p(gpu.current_stream_int())
+    v = rng.integers(0, nodes, size=centers).astype(np.int64)
+    pairs = np.concatenate([[-7, -7, -7], v, v + 1]).astype(np.int64)        # three elements of storage offset
+    d_pairs = torch.from_numpy(pairs).cuda()
+    out = torch.full((2 * centers + 5,), -1, dtype=torch.int64, device="cuda")
+    tab = wgb.MatrixDescription((len(row_ptr), 1), 1, 0, int(DT.DtInt64))
+    idd = wgb.ArrayDescription(2 * centers, 3, int(DT.DtInt64))
+    od = wgb.MatrixDescription((2 * centers, 1), 1, 5, int(DT.DtInt64))
+    rc = lib.wholegraph_b200_gather_from_handle(h_row, C.byref(tab), C.c_void_p(d_pairs.data_ptr()), C.byref(idd),
+                                                C.c_void_p(out.data_ptr()), C.byref(od), env, stream, -1)
+    assert rc == 0
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    assert np.all(got[:5] == -1)
+    assert np.array_equal(got[5:5 + centers], row_ptr[v]) and np.array_equal(got[5 + centers:], row_ptr[v + 1])
+    # column ids at sampled edge positions, int32 ids widened to int64 by the gather's cast
+    has_edges = v[degree[v] > 0]
+    edges = (row_ptr[has_edges] + rng.integers(0, 1 << 30, size=len(has_edges)) % degree[has_edges]).astype(np.int64)
+    d_edges = torch.from_numpy(edges).cuda()
+    dst = torch.zeros(len(edges), dtype=torch.int64, device="cuda")
+    tab = wgb.MatrixDescription((len(col), 1), 1, 0, int(DT.DtInt))
+    idd = wgb.ArrayDescription(len(edges), 0, int(DT.DtInt64))
+    od = wgb.MatrixDescription((len(edges), 1), 1, 0, int(DT.DtInt64))
+    rc = lib.wholegraph_b200_gather_from_handle(h_col, C.byref(tab), C.c_void_p(d_edges.data_ptr()), C.byref(idd),
+                                                C.c_void_p(dst.data_ptr()), C.byref(od), env, stream, -1)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(dst.cpu().numpy(), col[edges].astype(np.int64))
+    # argument checks
+    bad = wgb.MatrixDescription((len(edges), 1), 1, 0, int(DT.DtFloat))
+    assert lib.wholegraph_b200_gather_from_handle(h_col, C.byref(tab), C.c_void_p(d_edges.data_ptr()), C.byref(idd),
+                                                  C.c_void_p(dst.data_ptr()), C.byref(bad), env, stream, -1) == int(wgb.ErrorCode.LOGIC_ERROR)
+    assert lib.wholegraph_b200_gather_from_handle(None, C.byref(tab), None, C.byref(idd), None, C.byref(od), env, stream, -1) \
+        == int(wgb.ErrorCode.INVALID_INPUT)
+    wgb.destroy_wholegraph_tensor(t_row)
+    wgb.destroy_wholegraph_tensor(t_col)
+    wgb.destroy_communicator(comm)

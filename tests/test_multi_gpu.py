@@ -26,7 +26,7 @@ def _device_count():
 # summation chain per id), -peerpush writes gradient sums straight into the owner's arena region.
 SCENARIOS = ["continuous", "distributed", "distributed-keepdups", "distributed-hostcounts", "distributed-nccl", "chunked",
              "optimizer", "optimizer-nopresum", "optimizer-peerpush", "cache", "fileio", "unequal", "unequal-nccl",
-             "unequal-keepdups", "roundrobin", "stated-size"]
+             "unequal-keepdups", "roundrobin", "hosttable", "nodecache", "stated-size"]
 
 
 @pytest.mark.parametrize("scenario", SCENARIOS + ["all-in-one"])
