@@ -222,6 +222,8 @@ def _declare(lib: C.CDLL) -> None:
         "wholegraph_b200_embedding_get_cache_tensors": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
                                                                    C.POINTER(C.c_int)]),
         "wholegraph_b200_embedding_get_cache_counters": (C.c_int, [vp, C.POINTER(vp), C.POINTER(i64)]),
+        "wholegraph_b200_unique_by_owner_any_order": (C.c_int, [vp, C.c_int, i64, C.POINTER(i64), C.c_int, vp, sz,
+                                                                vp, vp, vp, vp, vp]),
         "wholegraph_b200_release_output": (C.c_int, [vp]),
         "graph_append_unique": (C.c_int, [vp, vp, vp, vp, C.POINTER(EnvFns), vp]),
         "csr_add_self_loop": (C.c_int, [vp, vp, vp, vp, vp]),

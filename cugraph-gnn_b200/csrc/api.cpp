@@ -396,7 +396,7 @@ size_t wholegraph_b200_unique_workspace_bytes(int64_t n, int64_t total_rows)
   return wgb::unique_workspace_bytes(n, total_rows);
 }
 
-wholegraph_error_code_t wholegraph_b200_unique_by_owner(const void* ids,
+static wholegraph_error_code_t unique_by_owner_entry(bool ascending, const char* where, const void* ids,
                                                           int ids_are_64,
                                                           int64_t n,
                                                           const int64_t* first_row,
@@ -419,9 +419,43 @@ wholegraph_error_code_t wholegraph_b200_unique_by_owner(const void* ids,
   if (!wgb::unique_supported(n, first_row[world])) return WHOLEGRAPH_INVALID_VALUE;
   if (workspace_bytes < wgb::unique_workspace_bytes(n, first_row[world])) return WHOLEGRAPH_INVALID_VALUE;
   wgb::unique_by_owner(ids, ids_are_64 != 0, n, first_row, world, workspace, unique_ids, inverse, counts,
-                       starts, static_cast<cudaStream_t>(stream));
+                       starts, static_cast<cudaStream_t>(stream), ascending);
   return WHOLEGRAPH_SUCCESS;
-  WGB_API_END("wholegraph_b200_unique_by_owner")
+  WGB_API_END(where)
+}
+
+wholegraph_error_code_t wholegraph_b200_unique_by_owner(const void* ids,
+                                                          int ids_are_64,
+                                                          int64_t n,
+                                                          const int64_t* first_row,
+                                                          int world,
+                                                          void* workspace,
+                                                          size_t workspace_bytes,
+                                                          int64_t* unique_ids,
+                                                          int64_t* inverse,
+                                                          int64_t* counts,
+                                                          int64_t* starts,
+                                                          void* stream)
+{
+  return unique_by_owner_entry(true, "wholegraph_b200_unique_by_owner", ids, ids_are_64, n, first_row, world, workspace,
+                               workspace_bytes, unique_ids, inverse, counts, starts, stream);
+}
+
+wholegraph_error_code_t wholegraph_b200_unique_by_owner_any_order(const void* ids,
+                                                                    int ids_are_64,
+                                                                    int64_t n,
+                                                                    const int64_t* first_row,
+                                                                    int world,
+                                                                    void* workspace,
+                                                                    size_t workspace_bytes,
+                                                                    int64_t* unique_ids,
+                                                                    int64_t* inverse,
+                                                                    int64_t* counts,
+                                                                    int64_t* starts,
+                                                                    void* stream)
+{
+  return unique_by_owner_entry(false, "wholegraph_b200_unique_by_owner_any_order", ids, ids_are_64, n, first_row, world,
+                               workspace, workspace_bytes, unique_ids, inverse, counts, starts, stream);
 }
 
 int wholegraph_b200_exchange_chunk_count(const int64_t* matrix, int world, size_t row_bytes, int wanted,

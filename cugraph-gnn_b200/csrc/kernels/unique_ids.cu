@@ -1,5 +1,10 @@
 // De-duplication of a gather's request list before it goes on the wire.
 //
+// Two implementations with the same outputs up to the order of the distinct ids inside an
+// owner's group (which nothing downstream depends on: every list position finds its id through
+// `inverse`).  Lists of up to 2^27 ids go through a hash table (four short kernels, below); longer
+// ones, or callers that ask for ascending ids, through a sort:
+//
 // A skewed request list (a GNN mini-batch hits hub nodes again and again) sends the same id to
 // the same owner many times; the owner of a hot row then serves - and its NVLink egress
 // carries - several times the average.  Sorting the ids once gives both the grouping by owner
@@ -130,6 +135,160 @@ layout layout_for(int64_t n, int64_t total_rows)
   return l;
 }
 
+// ---- hash-table variant ------------------------------------------------------------------------
+//   1. insert_kernel  every valid id claims (or finds) its entry of an open-addressing table of
+//                     at least 2 n entries; the claimer counts as one distinct id of its owner
+//   2. starts_kernel  exclusive scan of the per-owner counts
+//   3. place_kernel   claimers take the next slot of their owner's group and leave it in the entry
+//   4. inverse_kernel every list position reads its slot from its entry
+// A table entry is {id + 1, slot}; 0 marks an empty entry.  An id that is already in the table is
+// recognised with a plain load, so a hot id costs one compare-and-swap, not one per occurrence.
+struct owner_bounds {
+  int world;
+  int64_t first_row[kMaxPartitionRanks + 1];
+};
+
+__device__ __forceinline__ int owner_of_row(int64_t id, const int64_t* first_row, int world)
+{
+  int lo = 0, hi = world - 1;  // last rank whose first row is <= id
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (first_row[mid] <= id) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ uint32_t mix(uint32_t x)
+{
+  x ^= x >> 16;
+  x *= 0x7feb352du;
+  x ^= x >> 15;
+  x *= 0x846ca68bu;
+  x ^= x >> 16;
+  return x;
+}
+
+constexpr uint32_t kNoEntry    = 0xffffffffu;
+constexpr uint32_t kClaimedBit = 0x80000000u;
+
+__global__ void __launch_bounds__(kThreads)
+  insert_kernel(const void* ids, int is64, int64_t n, owner_bounds b, uint2* table, uint32_t table_mask,
+                uint32_t* entry_of, unsigned long long* owner_count)
+{
+  __shared__ int64_t s_first[kMaxPartitionRanks + 1];
+  for (int i = threadIdx.x; i <= b.world; i += kThreads) s_first[i] = b.first_row[i];
+  __syncthreads();
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  int owner       = b.world;  // b.world: nothing to count
+  if (i < n) {
+    const int64_t id = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
+                            : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
+    uint32_t where   = kNoEntry;
+    if (id >= 0 && id < s_first[b.world]) {
+      const uint32_t key = static_cast<uint32_t>(id) + 1u;
+      uint32_t s         = mix(key) & table_mask;
+      bool claimed       = false;
+      for (;;) {
+        uint32_t seen = __ldcg(&table[s].x);
+        if (seen == 0u) {
+          seen = atomicCAS(&table[s].x, 0u, key);
+          if (seen == 0u) {
+            claimed = true;
+            break;
+          }
+        }
+        if (seen == key) break;
+        s = (s + 1u) & table_mask;
+      }
+      where = s | (claimed ? kClaimedBit : 0u);
+      if (claimed) owner = owner_of_row(id, s_first, b.world);
+    }
+    entry_of[i] = where;
+  }
+  // one atomic per warp and owner
+  const unsigned peers = __match_any_sync(0xffffffffu, owner);
+  const int lane       = threadIdx.x & 31;
+  if (owner < b.world && lane == __ffs(peers) - 1)
+    atomicAdd(owner_count + owner, static_cast<unsigned long long>(__popc(peers)));
+}
+
+__global__ void starts_kernel(unsigned long long* owner_count, int world, int64_t* counts, int64_t* starts)
+{
+  if (threadIdx.x != 0) return;
+  int64_t run = 0;
+  for (int r = 0; r < world; r++) {
+    const int64_t c = static_cast<int64_t>(owner_count[r]);
+    counts[r]       = c;
+    starts[r]       = run;
+    owner_count[r]  = static_cast<unsigned long long>(run);  // becomes the group's fill cursor
+    run += c;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+  place_kernel(const void* ids, int is64, int64_t n, owner_bounds b, uint2* table, const uint32_t* entry_of,
+               unsigned long long* cursor, int64_t* unique_ids)
+{
+  __shared__ int64_t s_first[kMaxPartitionRanks + 1];
+  for (int i = threadIdx.x; i <= b.world; i += kThreads) s_first[i] = b.first_row[i];
+  __syncthreads();
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  int owner       = b.world;
+  int64_t id      = -1;
+  uint32_t where  = kNoEntry;
+  if (i < n) {
+    where = entry_of[i];
+    if (where != kNoEntry && (where & kClaimedBit) != 0u) {
+      id    = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
+                   : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
+      owner = owner_of_row(id, s_first, b.world);
+    }
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, owner);
+  const int lane       = threadIdx.x & 31;
+  const int leader     = __ffs(peers) - 1;
+  unsigned long long base = 0;
+  if (owner < b.world && lane == leader) base = atomicAdd(cursor + owner, static_cast<unsigned long long>(__popc(peers)));
+  base = __shfl_sync(0xffffffffu, base, leader);
+  if (owner < b.world) {
+    const int64_t slot = static_cast<int64_t>(base) + __popc(peers & ((1u << lane) - 1u));
+    unique_ids[slot]   = id;
+    table[where & ~kClaimedBit].y = static_cast<uint32_t>(slot);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+  inverse_kernel(int64_t n, const uint2* table, const uint32_t* entry_of, int64_t* inverse)
+{
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t where = entry_of[i];
+  inverse[i] = where == kNoEntry ? -1 : static_cast<int64_t>(__ldcg(&table[where & ~kClaimedBit].y));
+}
+
+struct hashed_layout {
+  size_t table, entry_of, owner_count, total;
+  uint32_t entries;
+};
+
+hashed_layout hashed_layout_for(int64_t n)
+{
+  hashed_layout l{};
+  auto align       = [](size_t x) { return (x + 255) / 256 * 256; };
+  uint32_t entries = 1024;
+  while (static_cast<int64_t>(entries) < 2 * n) entries <<= 1;
+  l.entries  = entries;
+  size_t off = 0;
+  l.table = off, off += align(static_cast<size_t>(entries) * sizeof(uint2));
+  l.owner_count = off, off += align(sizeof(unsigned long long) * (kMaxPartitionRanks + 1));
+  l.entry_of = off, off += align(static_cast<size_t>(std::max<int64_t>(n, 1)) * 4);
+  l.total = off;
+  return l;
+}
+
+constexpr int64_t kHashedLimit = int64_t(1) << 27;
+
 }  // namespace
 
 bool unique_supported(int64_t n, int64_t total_rows)
@@ -137,11 +296,15 @@ bool unique_supported(int64_t n, int64_t total_rows)
   return n < (int64_t(1) << 31) && total_rows < (int64_t(1) << 32) - 1;
 }
 
-size_t unique_workspace_bytes(int64_t n, int64_t total_rows) { return layout_for(n, total_rows).total; }
+size_t unique_workspace_bytes(int64_t n, int64_t total_rows)
+{
+  // room for either variant
+  return std::max(layout_for(n, total_rows).total, n <= kHashedLimit ? hashed_layout_for(n).total : size_t(0));
+}
 
 void unique_by_owner(const void* ids, bool ids_are_64, int64_t n, const int64_t* first_row, int world,
                      void* workspace, int64_t* unique_ids, int64_t* inverse, int64_t* counts,
-                     int64_t* starts, cudaStream_t stream)
+                     int64_t* starts, cudaStream_t stream, bool ascending)
 {
   WGB_EXPECTS(world >= 1 && world <= kMaxPartitionRanks, "world size %d exceeds %d", world, kMaxPartitionRanks);
   const int64_t total_rows = first_row[world];
@@ -149,6 +312,28 @@ void unique_by_owner(const void* ids, bool ids_are_64, int64_t n, const int64_t*
   if (n == 0) {
     WGB_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int64_t) * world, stream));
     WGB_CUDA_CHECK(cudaMemsetAsync(starts, 0, sizeof(int64_t) * world, stream));
+    return;
+  }
+  if (!ascending && n <= kHashedLimit) {
+    const hashed_layout l = hashed_layout_for(n);
+    char* ws              = static_cast<char*>(workspace);
+    auto* table           = reinterpret_cast<uint2*>(ws + l.table);
+    auto* entry_of        = reinterpret_cast<uint32_t*>(ws + l.entry_of);
+    auto* owner_count     = reinterpret_cast<unsigned long long*>(ws + l.owner_count);
+    // table and counters are adjacent: one clear
+    WGB_CUDA_CHECK(cudaMemsetAsync(ws + l.table, 0, l.entry_of - l.table, stream));
+    owner_bounds b;
+    b.world = world;
+    for (int r = 0; r <= world; r++) b.first_row[r] = first_row[r];
+    const unsigned blocks = static_cast<unsigned>((n + kThreads - 1) / kThreads);
+    insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, b, table, l.entries - 1, entry_of,
+                                                   owner_count);
+    starts_kernel<<<1, 32, 0, stream>>>(owner_count, world, counts, starts);
+    place_kernel<<<blocks, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, b, table, entry_of, owner_count,
+                                                  unique_ids);
+    inverse_kernel<<<blocks, kThreads, 0, stream>>>(n, table, entry_of, inverse);
+    count_kernel_launch(4);
+    WGB_LAUNCH_CHECK(stream);
     return;
   }
   const layout l        = layout_for(n, total_rows);

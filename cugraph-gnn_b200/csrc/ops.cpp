@@ -138,7 +138,9 @@ int64_t exchange_plan::max_total_recv() const
 
 bool ensure_peer_arena(wholegraph_comm_* comm, size_t bytes_per_rank, cudaStream_t stream)
 {
-  if (comm->world_size == 1 || comm->arena_unavailable || !comm->tuning.peer_exchange) return false;
+  if ((comm->world_size == 1 && !comm->tuning.single_rank_exchange) || comm->arena_unavailable ||
+      !comm->tuning.peer_exchange)
+    return false;
   if (comm->arena_idle == nullptr)
     WGB_CUDA_CHECK(cudaEventCreateWithFlags(&comm->arena_idle, cudaEventDisableTiming));
   if (comm->arena != nullptr && comm->arena_bytes >= bytes_per_rank) return true;
@@ -348,8 +350,8 @@ static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph
   const int64_t dim   = tab.sizes[1];
   // Rows travel as they are stored; where that would put more bytes on the wire than casting at
   // the owner (a narrower output dtype), the other path is taken.
-  if (!comm->tuning.sync_free || !comm->tuning.peer_exchange || comm->board == nullptr || comm->arena_unavailable ||
-      W > kMaxServeRanks || es_tab > es_out)
+  if (!comm->tuning.sync_free || !comm->tuning.peer_exchange || (comm->board == nullptr && W > 1) ||
+      comm->arena_unavailable || W > kMaxServeRanks || es_tab > es_out)
     return false;
   const size_t row_b = static_cast<size_t>(dim) * es_tab;
 
@@ -404,7 +406,8 @@ static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph
   temp_buffer workspace(env), inverse_buf(env);
   int64_t* inverse = static_cast<int64_t*>(inverse_buf.device(std::max<int64_t>(n, 1), WHOLEGRAPH_DT_INT64));
   void* ws         = workspace.device_bytes(unique_workspace_bytes(n, first_row[W]));
-  unique_by_owner(ids, ids_are_64, n, first_row.data(), W, ws, my_ids, inverse, my_header, my_header + W, stream);
+  unique_by_owner(ids, ids_are_64, n, first_row.data(), W, ws, my_ids, inverse, my_header, my_header + W, stream,
+                  /*ascending=*/false);
   timer.mark("unique");
   comm->stream_barrier(stream);  // every rank's header and ids are in place
   timer.mark("barrier");
@@ -471,7 +474,7 @@ void gather_distributed(wholegraph_handle_* h, const wholegraph_matrix_descripti
   g.dst_dt = od.dtype, g.dim = dim, g.indices_are_64 = true, g.sm_hint = sms;
 
   temp_buffer cache_ws(env), address_buf(env);
-  if (W == 1) {
+  if (W == 1 && !(comm->tuning.single_rank_exchange && cache == nullptr)) {
     g.dst = out, g.dst_stride = od.stride, g.dst_offset = od.storage_offset;
     g.indices = ids, g.indices_are_64 = ids_are_64, g.count = n;
     if (cache != nullptr) {
@@ -634,7 +637,7 @@ void scatter_distributed(const void* in, const wholegraph_matrix_description_t& 
   put.dst_offset = tab.storage_offset, put.dst_select = ROW_BY_INDEX;
   put.dim = dim, put.indices_are_64 = true, put.sm_hint = sms;
 
-  if (W == 1) {
+  if (W == 1 && !comm->tuning.single_rank_exchange) {
     put.src = in, put.src_stride = id_.stride, put.src_offset = id_.storage_offset;
     put.indices = ids, put.indices_are_64 = ids_are_64, put.count = n;
     launch_row_copy(put, stream);

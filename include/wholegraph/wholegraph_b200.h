@@ -138,6 +138,26 @@ wholegraph_error_code_t wholegraph_b200_unique_by_owner(const void* ids,
                                                           void* stream);
 
 /*
+ * The same de-duplication without the promise of ascending ids: the distinct ids of an owner's group come
+ * in whatever order a hash table's insertion races give (it may differ from call to call); counts, starts
+ * and the meaning of `inverse` are unchanged.  Several times cheaper than the sorted form and what the
+ * distributed gather uses, since only `inverse` ties list positions to slots.  Lists longer than 2^27 ids
+ * fall back to the sorted form.
+ */
+wholegraph_error_code_t wholegraph_b200_unique_by_owner_any_order(const void* ids,
+                                                                    int ids_are_64,
+                                                                    int64_t n,
+                                                                    const int64_t* first_row,
+                                                                    int world,
+                                                                    void* workspace,
+                                                                    size_t workspace_bytes,
+                                                                    int64_t* unique_ids,
+                                                                    int64_t* inverse,
+                                                                    int64_t* counts,
+                                                                    int64_t* starts,
+                                                                    void* stream);
+
+/*
  * Number of chunks a pipelined NCCL row exchange runs in (no counterpart in the reference, whose
  * exchange is one alltoallv, exchange_embeddings_nccl_func.cu:23-64).  Every chunk is a matched set
  * of sends and receives, so all ranks must arrive at the same number: it is a function of the

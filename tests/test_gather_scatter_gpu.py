@@ -371,3 +371,56 @@ def test_gather_from_a_handle_with_raw_pointers(gpu, wgb, orc, mem_name):
     wgb.destroy_wholegraph_tensor(t_row)
     wgb.destroy_wholegraph_tensor(t_col)
     wgb.destroy_communicator(comm)
+
+
+@pytest.mark.parametrize("switches", [{}, {"WG_SYNC_FREE": "0"}, {"WG_PEER_EXCHANGE": "0"}, {"WG_GATHER_DEDUP": "0"},
+                                      {"WG_GATHER_DEDUP": "0", "WG_PEER_EXCHANGE": "0", "WG_EXCHANGE_CHUNKS": "3"}],
+                         ids=["sync-free", "host-counts", "nccl-rows", "keep-duplicates", "keep-duplicates-chunked"])
+@pytest.mark.parametrize("tab_dt,out_dt,dim", [(4, 4, 128), (2, 1, 33), (1, 2, 64), (6, 6, 5)])
+def test_distributed_exchange_code_on_one_rank(gpu, wgb, orc, monkeypatch, switches, tab_dt, out_dt, dim):
+    """WG_SINGLE_RANK_EXCHANGE=1 makes a one-rank communicator run the exchange code of a DISTRIBUTED
+    gather and scatter - de-duplication, request header and ids in the exchange arena, the owner's
+    serve kernel, the expansion, or the routed / chunked variants the other switches select - with
+    itself as its only peer, so that this code is checked against the oracle on one GPU as well.
+    (The reference runs its distributed path on one rank the same way: on a one-GPU box its gtests
+    degenerate to world size 1, cpp/tests/wholegraph_tensor_ops/wholegraph_gather_tests.cu:126-269.)"""
+    import torch
+    MT, ML, DT = wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphDataType
+    monkeypatch.setenv("WG_SINGLE_RANK_EXCHANGE", "1")
+    for k, v in switches.items():
+        monkeypatch.setenv(k, v)
+    comm = wgb.create_communicator(wgb.UniqueId(), 0, 1)      # reads the switches
+    rng = np.random.default_rng(tab_dt * 100 + out_dt + dim)
+    rows = 30_011
+    table_np = _random_table(rng, orc, rows, dim, tab_dt)
+    t = wgb.create_wholegraph_tensor(wgb.make_description([rows, dim], DT(tab_dt)), comm, MT.MtDistributed, ML.MlDevice)
+    gpu.write_local_shard(t, _to_device(torch, table_np, tab_dt).contiguous())
+    launches = wgb.lib().wholegraph_b200_kernel_launch_count()
+    for n in (12_345, 0, 1, 40_000):
+        idx = rng.integers(0, rows, size=n).astype(np.int64)
+        if n > 10:
+            idx[: n // 3] = idx[n // 3: 2 * (n // 3)]            # duplicates
+            idx[::37] = -1
+            idx[5] = rows + 3                                    # nobody's row: left untouched
+        sentinel = _random_table(rng, orc, max(n, 1), dim, out_dt)[:n]
+        d_out = _to_device(torch, sentinel.copy(), out_dt)
+        gpu.gather(t, torch.from_numpy(idx).cuda(), d_out)
+        torch.cuda.synchronize()
+        want = sentinel.copy()
+        orc.gather(table_np, np.where(idx >= rows, -1, idx), out_dt=out_dt, out=want, table_bf16=(tab_dt == 4))
+        assert np.array_equal(_to_host(torch, d_out, out_dt).view(want.dtype), want), f"n={n}"
+    if not switches:
+        assert wgb.lib().wholegraph_b200_kernel_launch_count() - launches >= 3 * 6   # not the one-kernel shortcut
+    # scatter through the routed exchange, then read back
+    n = 9_000
+    perm = rng.permutation(rows)[:n].astype(np.int64)
+    rows_in = _random_table(rng, orc, n, dim, out_dt)
+    gpu.scatter(_to_device(torch, rows_in, out_dt), torch.from_numpy(perm).cuda(), t)
+    back = _to_device(torch, np.zeros_like(table_np), tab_dt)
+    gpu.gather(t, torch.arange(rows, device="cuda", dtype=torch.int64), back)
+    torch.cuda.synchronize()
+    want_table = table_np.copy()
+    orc.scatter(rows_in, perm, want_table, rows_bf16=(out_dt == 4), table_bf16=(tab_dt == 4))
+    assert np.array_equal(_to_host(torch, back, tab_dt).view(want_table.dtype), want_table)
+    wgb.destroy_wholegraph_tensor(t)
+    wgb.destroy_communicator(comm)
