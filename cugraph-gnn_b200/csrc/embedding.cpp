@@ -488,6 +488,113 @@ wholegraph_error_code_t create_states(wholegraph_embedding_* e)
   return WHOLEGRAPH_SUCCESS;
 }
 
+// Gradient apply over several ranks with nothing sized on the host: every rank adds up its own
+// duplicates (as in the default path) but leaves the sums in ITS OWN region of the peer-mapped
+// arena, together with its distinct ids and the number of them it has for every owner; after a
+// barrier in stream order every owner merges what the senders hold for it (merged_apply: bitmaps
+// over its rows instead of a sort) and reads the sums rows straight from the senders' regions
+// while it updates its rows - transfer and update are one kernel.  The order of additions is that
+// of the default path: per rank in arrival order, then the per-rank sums in rank order.  Returns
+// false, on every rank alike and before anything was enqueued, when the path does not apply.
+bool gradient_apply_sync_free(wholegraph_embedding_* e, const sparse_apply_args& shard, const void* ids, bool ids_are_64,
+                              int64_t n, const float* g, int64_t g_stride, const std::vector<int64_t>& first_row,
+                              wholegraph_env_func_t* env, cudaStream_t stream)
+{
+  auto* comm   = e->comm;
+  const int W  = comm->world_size;
+  const int me = comm->world_rank;
+  if (!comm->tuning.sync_free || !comm->tuning.gradient_presum || !comm->tuning.peer_exchange ||
+      (comm->board == nullptr && W > 1) || comm->arena_unavailable || W > kMaxMergeRanks ||
+      shard.weight_cache.tags != nullptr || shard.state_cache.tags != nullptr)
+    return false;
+  int64_t widest = 0;  // rows of the largest shard: the merge bitmaps must stay small
+  for (int r = 0; r < W; r++) widest = std::max(widest, first_row[r + 1] - first_row[r]);
+  if (widest >= (int64_t(1) << 31) || static_cast<int64_t>(W) * ((widest + 31) / 32) > (int64_t(1) << 27)) return false;
+  const size_t row_b = static_cast<size_t>(e->dim) * sizeof(float);
+
+  int64_t mine[wholegraph_comm_::kBoardValues] = {n, e->dim, static_cast<int64_t>(shard.hyper.type),
+                                                  reduce_duplicates_supported(n, first_row[W], W) ? 1 : 0,
+                                                  static_cast<int64_t>(wholegraph_tensor_get_memory_handle(e->allocated)->id),
+                                                  0x67726164 /* "grad" */};
+  std::vector<int64_t> all(static_cast<size_t>(W) * wholegraph_comm_::kBoardValues);
+  comm->board_exchange(mine, all.data());
+  int64_t capacity = 1, total_n = 0;
+  bool supported   = true;
+  for (int r = 0; r < W; r++) {
+    const int64_t* v = all.data() + static_cast<size_t>(r) * wholegraph_comm_::kBoardValues;
+    WGB_EXPECTS(v[1] == mine[1] && v[2] == mine[2] && v[4] == mine[4] && v[5] == mine[5],
+                "rank %d is in another collective call than rank %d (gradient apply)", r, me);
+    capacity  = std::max(capacity, v[0]);
+    total_n += v[0];
+    supported = supported && v[3] != 0;
+  }
+  if (!supported) return false;
+  auto ids_offset  = []() { return size_t(2) * sizeof(int64_t) * kMaxMergeRanks; };
+  auto sums_offset = [&](int64_t cap) { return ids_offset() + (static_cast<size_t>(cap) * 8 + 255) / 256 * 256; };
+  auto region_size = [&](int64_t cap) { return sums_offset(cap) + static_cast<size_t>(cap) * row_b; };
+  if (!ensure_peer_arena(comm, region_size(capacity), stream)) return false;
+  {  // every rank derives the same capacity from the arena's size
+    int64_t most = (static_cast<int64_t>(comm->arena_bytes) - static_cast<int64_t>(ids_offset()) - 256) /
+                   static_cast<int64_t>(row_b + 8);
+    most = std::min<int64_t>(most, (int64_t(1) << 31) - 2);
+    while (most > capacity && region_size(most) > comm->arena_bytes) most--;
+    capacity = std::max(capacity, most);
+  }
+  if (comm->status_word == nullptr) {
+    WGB_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&comm->status_word), 256));
+    WGB_CUDA_CHECK(cudaMemset(comm->status_word, 0, 256));
+    WGB_CUDA_CHECK(cudaMallocHost(reinterpret_cast<void**>(&comm->status_host), 64));
+    *comm->status_host = 0;
+  }
+  if (*comm->status_host != 0) {
+    *comm->status_host = 0;
+    WGB_CUDA_CHECK(cudaMemsetAsync(comm->status_word, 0, sizeof(int), stream));
+    throw comm_error("an earlier distributed op refused ids or sizes a peer had left for this rank");
+  }
+
+  phase_timer timer(stream);
+  timer.mark("start");
+  char* region     = peer_arena_region(comm, me);
+  int64_t* header  = reinterpret_cast<int64_t*>(region);
+  int64_t* uids    = reinterpret_cast<int64_t*>(region + ids_offset());
+  float* sums      = reinterpret_cast<float*>(region + sums_offset(capacity));
+  temp_buffer presum_ws(env), merge_ws(env);
+  if (n > 0) {
+    void* pws = presum_ws.device_bytes(reduce_duplicates_workspace_bytes(n, first_row[W], e->dim));
+    reduce_duplicates_group(ids, ids_are_64, n, e->dim, first_row.data(), W, pws, uids, header, header + W, stream);
+    timer.mark("group");
+    // the sums of the k-th distinct id go to row k: one destination, whatever its owner
+    const int64_t everything = n;
+    float* dest              = sums;
+    reduce_duplicates_sum(n, first_row[W], g, g_stride, e->dim, 1, &everything, &dest, pws, stream);
+    timer.mark("presum");
+  } else {
+    WGB_CUDA_CHECK(cudaMemsetAsync(header, 0, sizeof(int64_t) * 2 * W, stream));
+  }
+  comm->stream_barrier(stream);  // every sender's header, ids and sums are in place
+  timer.mark("barrier");
+
+  merged_apply_args m;
+  m.world = W, m.me = me;
+  for (int r = 0; r < W; r++) {
+    char* rr           = peer_arena_region(comm, r);
+    m.sender[r].header = reinterpret_cast<const int64_t*>(rr);
+    m.sender[r].ids    = reinterpret_cast<const int64_t*>(rr + ids_offset());
+    m.sender[r].sums   = reinterpret_cast<const float*>(rr + sums_offset(capacity));
+  }
+  m.capacity            = capacity;
+  m.entries_upper_bound = std::min<int64_t>(total_n, static_cast<int64_t>(W) * shard.local_rows);
+  m.status              = comm->status_word;
+  m.shard               = shard;
+  merged_apply(m, merge_ws.device_bytes(merged_apply_workspace_bytes(W, shard.local_rows, m.entries_upper_bound)), stream);
+  timer.mark("merge+apply");
+  comm->stream_barrier(stream);  // nobody reads a sender's region any more
+  WGB_CUDA_CHECK(cudaMemcpyAsync(comm->status_host, comm->status_word, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));
+  timer.mark("barrier");
+  return true;
+}
+
 // Backward step on already-mapped ids.
 void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, wholegraph_tensor_t grads,
                     bool adjust_cache, float lr, wholegraph_env_func_t* env, cudaStream_t stream)
@@ -550,7 +657,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   };
 
   temp_buffer ws(env);
-  if (W == 1) {
+  if (W == 1 && !(comm->tuning.single_rank_exchange && a.weight_cache.tags == nullptr && a.state_cache.tags == nullptr)) {
     if (n == 0) return;
     a.ids = ids, a.ids_are_64 = ids_are_64, a.count = n;
     a.grads = g, a.grad_stride = gd->strides[0];
@@ -566,6 +673,7 @@ void gradient_apply(wholegraph_embedding_* e, wholegraph_tensor_t indices, whole
   temp_buffer send_buf(env), recv_buf(env), uid_buf(env), counts_buf(env), presum_ws(env);
   // A call on another stream may still be reading this rank's arena region.
   if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->arena_idle, 0));
+  if (gradient_apply_sync_free(e, a, ids, ids_are_64, n, g, gd->strides[0], first_row, env, stream)) return;
   char* recv = nullptr;
   phase_timer timer(stream);
   timer.mark("start");

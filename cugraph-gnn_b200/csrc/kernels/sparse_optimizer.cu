@@ -25,8 +25,10 @@
 
 #include <algorithm>
 #include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
 #include <cub/device/device_select.cuh>
 #include <thrust/iterator/counting_iterator.h>
+#include <thrust/iterator/transform_iterator.h>
 
 #include "../common.hpp"
 #include "row_copy.hpp"
@@ -800,6 +802,306 @@ void reduce_duplicates_sum(int64_t count, int64_t table_rows, const float* grads
   p.owner_first_run[world] = static_cast<int32_t>(first);
   launch_apply_opt<float>(p, vec4, apply_grid(count), stream);
   count_kernel_launch(3);
+  WGB_LAUNCH_CHECK(stream);
+}
+
+// ---- merged apply: per-rank sums read from their senders' regions --------------------------------
+namespace {
+
+struct merge_params {
+  int world, me;
+  int64_t capacity;
+  int64_t local_start, local_rows;
+  int words;                 // 32-bit bitmap words per sender
+  uint32_t* bitmap;          // [world][words]
+  int32_t* rank;             // [world * words + 1] exclusive prefix of popcounts
+  int32_t* heads;            // rows some sender touched
+  int32_t* head_count;
+  int* status;
+  int dim;
+  void* weights;
+  int64_t weight_stride;
+  float* state;
+  int64_t state_stride, v_offset;
+  float* beta12t;
+  optimizer_hyper h;
+  sender_region sender[kMaxMergeRanks];
+};
+
+// Group of this rank in sender q's lists: counts[me] ids starting at starts[me]; refused (and
+// treated as empty) when it does not fit the region.
+__device__ __forceinline__ void read_group(const merge_params& p, int q, int64_t* count, int64_t* start)
+{
+  const int64_t* h = p.sender[q].header;
+  int64_t c        = __ldcg(h + p.me);
+  const int64_t s  = __ldcg(h + p.world + p.me);
+  if (c < 0 || s < 0 || s + c > p.capacity) {
+    atomicExch(p.status, 1);
+    c = 0;
+  }
+  *count = c, *start = s;
+}
+
+__global__ void __launch_bounds__(kThreads) merge_mark_kernel(const merge_params p)
+{
+  __shared__ int64_t s_prefix[kMaxMergeRanks + 1];
+  __shared__ int64_t s_start[kMaxMergeRanks];
+  if (threadIdx.x < p.world) {
+    int64_t c, s;
+    read_group(p, threadIdx.x, &c, &s);
+    s_start[threadIdx.x]      = s;
+    s_prefix[threadIdx.x + 1] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_prefix[0] = 0;
+    for (int q = 0; q < p.world; q++) s_prefix[q + 1] += s_prefix[q];
+  }
+  __syncthreads();
+  const int64_t total = s_prefix[p.world];
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int q = 0;
+    while (q + 1 < p.world && i >= s_prefix[q + 1]) q++;
+    const int64_t id  = __ldcg(p.sender[q].ids + s_start[q] + (i - s_prefix[q]));
+    const int64_t row = id - p.local_start;
+    if (row < 0 || row >= p.local_rows) {
+      atomicExch(p.status, 2);
+      continue;
+    }
+    atomicOr(p.bitmap + static_cast<int64_t>(q) * p.words + (row >> 5), 1u << (row & 31));
+  }
+}
+
+struct popcount_of {
+  const uint32_t* words;
+  __device__ __forceinline__ int operator()(int i) const { return __popc(words[i]); }
+};
+
+// Rows with a bit in any sender's bitmap, ascending inside a warp's 32 words.
+__global__ void __launch_bounds__(kThreads) merge_heads_kernel(const merge_params p)
+{
+  const int lane = threadIdx.x & 31;
+  for (int64_t w0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) & ~int64_t(31); w0 < p.words;
+       w0 += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t w = w0 + lane;
+    uint32_t any    = 0;
+    if (w < p.words)
+      for (int q = 0; q < p.world; q++) any |= p.bitmap[static_cast<int64_t>(q) * p.words + w];
+    const int mine = __popc(any);
+    int incl       = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += v;
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (total == 0) continue;
+    int base = 0;
+    if (lane == 31) base = atomicAdd(p.head_count, total);
+    base    = __shfl_sync(0xffffffffu, base, 31);
+    int out = base + incl - mine;
+    while (any != 0u) {
+      const int bit  = __ffs(any) - 1;
+      p.heads[out++] = static_cast<int32_t>(w * 32 + bit);
+      any &= any - 1u;
+    }
+  }
+}
+
+constexpr int kMergeFlight = 4;  // senders' rows in flight per lane (for two column groups)
+
+template <int OPT, typename W, int VEC>
+__global__ void __launch_bounds__(kThreads, 2) merge_apply_kernel(const merge_params p)
+{
+  __shared__ int64_t s_start[kMaxMergeRanks];
+  if (threadIdx.x < p.world) {
+    int64_t c, s;
+    read_group(p, threadIdx.x, &c, &s);
+    s_start[threadIdx.x] = s;
+  }
+  __syncthreads();
+  constexpr unsigned kFull  = 0xffffffffu;
+  const int lane            = threadIdx.x & 31;
+  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int heads           = *p.head_count;
+  W* weights                = static_cast<W*>(p.weights);
+  for (int64_t hd = warp_global; hd < heads; hd += warp_stride) {
+    const int row = p.heads[hd];
+    // lane q: does sender q hold this row, and where
+    const float* src = nullptr;
+    if (lane < p.world) {
+      const int64_t wi    = static_cast<int64_t>(lane) * p.words + (row >> 5);
+      const uint32_t word = p.bitmap[wi];
+      if ((word >> (row & 31)) & 1u) {
+        const int64_t pos = p.rank[wi] - p.rank[static_cast<int64_t>(lane) * p.words] +
+                            __popc(word & ((1u << (row & 31)) - 1u));
+        src = p.sender[lane].sums + (s_start[lane] + pos) * p.dim;
+      }
+    }
+    unsigned senders = __ballot_sync(kFull, src != nullptr);
+    float beta1t = 0.f, beta2t = 0.f;
+    if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
+      // per-row running beta1^t, beta2^t: multiplied on every touch of the row
+      float2 v = make_float2(0.f, 0.f);
+      if (lane == 0) {
+        float2* b = reinterpret_cast<float2*>(p.beta12t) + row;
+        v         = *b;
+        v.x       = __fmul_rn(v.x, p.h.beta1);
+        v.y       = __fmul_rn(v.y, p.h.beta2);
+        *b        = v;
+      }
+      beta1t = __shfl_sync(kFull, v.x, 0);
+      beta2t = __shfl_sync(kFull, v.y, 0);
+    }
+    W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
+    float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
+    apply_params ap{};  // the fields row_columns reads
+    ap.v_offset = p.v_offset, ap.h = p.h;
+    for (int cb = 0; cb < p.dim; cb += 64 * VEC) {
+      const int c0 = cb + lane * VEC, c1 = c0 + 32 * VEC;
+      const bool on0 = c0 < p.dim, on1 = c1 < p.dim;
+      float acc0[VEC] = {}, acc1[VEC] = {};
+      row_columns<OPT, W, VEC> x0, x1;
+      x0.load(ap, w_row, s_row, c0, on0);
+      x1.load(ap, w_row, s_row, c1, on1);
+      unsigned left = senders;
+      bool first    = true;
+      while (left != 0u) {
+        float v0[kMergeFlight][VEC], v1[kMergeFlight][VEC];
+        bool live[kMergeFlight];
+#pragma unroll
+        for (int u = 0; u < kMergeFlight; u++) {
+          live[u]     = left != 0u;
+          const int q = live[u] ? __ffs(left) - 1 : 0;
+          if (live[u]) left &= left - 1u;
+          const float* g = reinterpret_cast<const float*>(
+            __shfl_sync(kFull, reinterpret_cast<unsigned long long>(src), q));
+          load_grad<VEC>(g + c0, live[u] && on0, v0[u]);
+          load_grad<VEC>(g + c1, live[u] && on1, v1[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < kMergeFlight; u++) {
+          if (live[u]) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) {
+              acc0[e] = first ? v0[u][e] : __fadd_rn(acc0[e], v0[u][e]);
+              acc1[e] = first ? v1[u][e] : __fadd_rn(acc1[e], v1[u][e]);
+            }
+            first = false;
+          }
+        }
+      }
+      x0.update_and_store(ap, w_row, s_row, c0, on0, acc0, beta1t, beta2t);
+      x1.update_and_store(ap, w_row, s_row, c1, on1, acc1, beta1t, beta2t);
+    }
+  }
+}
+
+struct merge_layout {
+  size_t bitmap, rank, heads, counters, cub, total, cub_bytes;
+  int words;
+};
+
+merge_layout merge_layout_for(int world, int64_t local_rows, int64_t entries_upper_bound)
+{
+  merge_layout l{};
+  auto align = [](size_t x) { return (x + 255) / 256 * 256; };
+  l.words    = static_cast<int>((local_rows + 31) / 32);
+  size_t off = 0;
+  const size_t all_words = static_cast<size_t>(world) * static_cast<size_t>(std::max(l.words, 1));
+  l.bitmap = off, off += align(all_words * 4);
+  l.counters = off, off += 256;
+  l.rank = off, off += align((all_words + 1) * 4);
+  l.heads = off, off += align(static_cast<size_t>(std::max<int64_t>(1, std::min(local_rows, entries_upper_bound))) * 4);
+  l.cub_bytes = 0;
+  auto counts = thrust::make_transform_iterator(thrust::counting_iterator<int>(0), popcount_of{nullptr});
+  cub::DeviceScan::ExclusiveSum(nullptr, l.cub_bytes, counts, static_cast<int32_t*>(nullptr),
+                                static_cast<int>(all_words + 1));
+  l.cub = off, off += align(l.cub_bytes);
+  l.total = off;
+  return l;
+}
+
+template <int OPT, typename W>
+void launch_merge_apply(const merge_params& p, bool vec4, cudaStream_t stream)
+{
+  const int ctas = sm_count() * 2;
+  if (vec4)
+    merge_apply_kernel<OPT, W, 4><<<ctas, kThreads, 0, stream>>>(p);
+  else
+    merge_apply_kernel<OPT, W, 1><<<ctas, kThreads, 0, stream>>>(p);
+}
+
+template <typename W>
+void launch_merge_apply_opt(const merge_params& p, bool vec4, cudaStream_t stream)
+{
+  switch (p.h.type) {
+    case WHOLEGRAPH_OPT_SGD: launch_merge_apply<WHOLEGRAPH_OPT_SGD, W>(p, vec4, stream); break;
+    case WHOLEGRAPH_OPT_LAZY_ADAM: launch_merge_apply<WHOLEGRAPH_OPT_LAZY_ADAM, W>(p, vec4, stream); break;
+    case WHOLEGRAPH_OPT_ADAGRAD: launch_merge_apply<WHOLEGRAPH_OPT_ADAGRAD, W>(p, vec4, stream); break;
+    case WHOLEGRAPH_OPT_RMSPROP: launch_merge_apply<WHOLEGRAPH_OPT_RMSPROP, W>(p, vec4, stream); break;
+    default: WGB_EXPECTS(false, "unknown optimizer type %d", (int)p.h.type);
+  }
+}
+
+}  // namespace
+
+size_t merged_apply_workspace_bytes(int world, int64_t local_rows, int64_t entries_upper_bound)
+{
+  return merge_layout_for(world, local_rows, entries_upper_bound).total;
+}
+
+void merged_apply(const merged_apply_args& a, void* workspace, cudaStream_t stream)
+{
+  const sparse_apply_args& sh = a.shard;
+  WGB_EXPECTS(a.world >= 1 && a.world <= kMaxMergeRanks, "world size %d exceeds %d", a.world, kMaxMergeRanks);
+  WGB_EXPECTS(a.status != nullptr, "merged apply needs a status word");
+  WGB_EXPECTS(sh.local_rows < (int64_t(1) << 31) && static_cast<int64_t>(a.world) * ((sh.local_rows + 31) / 32) < (int64_t(1) << 31) - 2,
+              "shard too large for the merge bitmaps");
+  WGB_EXPECTS(sh.weight_cache.tags == nullptr && sh.state_cache.tags == nullptr, "merged apply does not go through caches");
+  WGB_EXPECTS(sh.hyper.type == WHOLEGRAPH_OPT_SGD || sh.state != nullptr, "optimizer state is missing");
+  WGB_EXPECTS(sh.hyper.type != WHOLEGRAPH_OPT_LAZY_ADAM || sh.beta12t != nullptr, "beta12t is missing");
+  if (sh.local_rows == 0 || sh.dim == 0 || a.entries_upper_bound <= 0) return;
+  const merge_layout l = merge_layout_for(a.world, sh.local_rows, a.entries_upper_bound);
+  char* ws             = static_cast<char*>(workspace);
+  merge_params p{};
+  p.world = a.world, p.me = a.me, p.capacity = a.capacity;
+  p.local_start = sh.local_start, p.local_rows = sh.local_rows;
+  p.words      = l.words;
+  p.bitmap     = reinterpret_cast<uint32_t*>(ws + l.bitmap);
+  p.rank       = reinterpret_cast<int32_t*>(ws + l.rank);
+  p.heads      = reinterpret_cast<int32_t*>(ws + l.heads);
+  p.head_count = reinterpret_cast<int32_t*>(ws + l.counters);
+  p.status     = a.status;
+  p.dim = static_cast<int>(sh.dim), p.weights = sh.weights, p.weight_stride = sh.weight_stride;
+  p.state = sh.state, p.state_stride = sh.state_stride, p.v_offset = sh.v_offset, p.beta12t = sh.beta12t;
+  p.h = sh.hyper;
+  for (int q = 0; q < a.world; q++) p.sender[q] = a.sender[q];
+  // bitmaps and the head counter sit next to each other: one clear
+  WGB_CUDA_CHECK(cudaMemsetAsync(ws + l.bitmap, 0, l.rank - l.bitmap, stream));
+  const int64_t mark_ctas = std::min<int64_t>((a.entries_upper_bound + kThreads - 1) / kThreads, sm_count() * 16);
+  merge_mark_kernel<<<static_cast<unsigned>(std::max<int64_t>(1, mark_ctas)), kThreads, 0, stream>>>(p);
+  const size_t all_words = static_cast<size_t>(a.world) * static_cast<size_t>(l.words);
+  auto counts = thrust::make_transform_iterator(thrust::counting_iterator<int>(0), popcount_of{p.bitmap});
+  size_t cub_bytes = l.cub_bytes;
+  // one entry past the bitmaps (the zeroed counter word) closes the last sender's prefix
+  WGB_CUDA_CHECK(cub::DeviceScan::ExclusiveSum(ws + l.cub, cub_bytes, counts, p.rank, static_cast<int>(all_words + 1), stream));
+  const int64_t head_ctas = std::min<int64_t>((l.words + kThreads - 1) / kThreads, sm_count() * 16);
+  merge_heads_kernel<<<static_cast<unsigned>(std::max<int64_t>(1, head_ctas)), kThreads, 0, stream>>>(p);
+  const size_t w_es = wholegraph_dtype_get_element_size(sh.weight_dtype);
+  bool vec4 = sh.dim % 4 == 0 && sh.weight_stride % 4 == 0 && reinterpret_cast<uintptr_t>(sh.weights) % (4 * w_es) == 0 &&
+              (sh.state == nullptr || (sh.state_stride % 4 == 0 && sh.v_offset % 4 == 0 &&
+                                       reinterpret_cast<uintptr_t>(sh.state) % 16 == 0));
+  for (int q = 0; q < a.world; q++) vec4 = vec4 && reinterpret_cast<uintptr_t>(a.sender[q].sums) % 16 == 0;
+  if (sh.weight_dtype == WHOLEGRAPH_DT_FLOAT)
+    launch_merge_apply_opt<float>(p, vec4, stream);
+  else if (sh.weight_dtype == WHOLEGRAPH_DT_HALF)
+    launch_merge_apply_opt<__half>(p, vec4, stream);
+  else
+    launch_merge_apply_opt<__nv_bfloat16>(p, vec4, stream);
+  count_kernel_launch(4);
   WGB_LAUNCH_CHECK(stream);
 }
 

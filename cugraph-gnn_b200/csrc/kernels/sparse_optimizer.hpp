@@ -92,6 +92,36 @@ void reduce_duplicates_sum(int64_t count, int64_t table_rows, const float* grads
                            int world, const int64_t* owner_counts, float* const* owner_out, void* workspace,
                            cudaStream_t stream);
 
+// Owner-side half of the two-level reduction when the per-rank sums stay where their senders
+// computed them: every sender's region (mapped here: peer memory over NVLink, or local) holds a
+// header, its distinct ids grouped by owner and one row of sums per id, and this rank merges and
+// applies them without any count ever reaching the host and without a sort:
+//   1. mark       every id sent here sets bit (row) in its sender's bitmap over this shard's rows
+//   2. rank       exclusive prefix of the bitmaps' popcounts: a row's position in a sender's list
+//                 is then two loads away (ids ascend inside a sender's group)
+//   3. heads      the rows some sender touched, compacted
+//   4. apply      one warp per such row: the senders that hold it, in rank order; their sums rows
+//                 are read straight from the senders' regions while weights and state are read
+//                 locally; sums added in rank order, then the same update as sparse_apply
+// Results are those of sparse_apply on the concatenation of the senders' lists in rank order.
+constexpr int kMaxMergeRanks = 32;
+struct sender_region {
+  const int64_t* header = nullptr;  // 2 * world int64: counts per owner | group starts
+  const int64_t* ids    = nullptr;  // distinct ids, grouped by owner, ascending inside a group
+  const float* sums     = nullptr;  // row k: the sums for ids[k], `dim` floats
+};
+struct merged_apply_args {
+  int world = 1, me = 0;
+  sender_region sender[kMaxMergeRanks];  // by rank
+  int64_t capacity            = 0;       // ids a region can hold; headers claiming more are refused
+  int64_t entries_upper_bound = 0;       // no more than this many ids are sent here in total
+  int* status                 = nullptr; // device word, set non-zero on a refused header or id
+  // the shard and the optimizer, as in sparse_apply_args (ids / grads / caches unused)
+  sparse_apply_args shard;
+};
+size_t merged_apply_workspace_bytes(int world, int64_t local_rows, int64_t entries_upper_bound);
+void merged_apply(const merged_apply_args& a, void* workspace, cudaStream_t stream);
+
 // Fill `count` floats with `value` (state initialisation).
 void fill_float(float* data, float value, int64_t count, cudaStream_t stream);
 

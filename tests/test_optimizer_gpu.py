@@ -229,3 +229,62 @@ def test_round_robin_embedding_gather_and_apply(gpu, wgb, orc, comm, rr, rows):
     assert np.array_equal(got, want)
     wgb.destroy_embedding(emb)
     wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
+
+
+@pytest.mark.parametrize("switches", [{}, {"WG_SYNC_FREE": "0"}, {"WG_SYNC_FREE": "0", "WG_PEER_GRADIENT": "1"},
+                                      {"WG_GRADIENT_PRESUM": "0"}],
+                         ids=["merged", "presum-exchange", "presum-peer-push", "every-row-routed"])
+@pytest.mark.parametrize("opt_name,table_dtype,dim", [("adam", "f32", 256), ("adam", "f32", 33), ("sgd", "bf16", 100),
+                                                      ("adagrad", "f16", 64), ("rmsprop", "f32", 392)])
+def test_multi_rank_gradient_code_on_one_rank(gpu, wgb, orc, monkeypatch, switches, opt_name, table_dtype, dim):
+    """WG_SINGLE_RANK_EXCHANGE=1: a one-rank communicator runs the multi-rank gradient path - the
+    per-rank pre-sum left in the exchange arena and the owner's merge (bitmaps, ranks, one warp per
+    touched row reading the senders' sums), or the routed variants the other switches select - with
+    itself as its only peer, so that this code is checked against the oracle on one GPU as well."""
+    monkeypatch.setenv("WG_SINGLE_RANK_EXCHANGE", "1")
+    for k, v in switches.items():
+        monkeypatch.setenv(k, v)
+    c = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+    try:
+        _run(gpu, wgb, orc, c, opt_name, 4096, dim, table_dtype, np.int64, 3, 3000, {"weight_decay": 0.01},
+             wgb.WholeGraphMemoryType.MtDistributed, block=256)
+    finally:
+        wgb.destroy_communicator(c)
+
+
+def test_merged_gradient_path_with_a_run_longer_than_a_block(gpu, wgb, orc, monkeypatch):
+    """One id takes a third of 6,000 gradient rows: the sender's pre-sum cuts it into blocks of 256,
+    the owner's merge then sees one row of sums for it."""
+    import torch
+    monkeypatch.setenv("WG_SINGLE_RANK_EXCHANGE", "1")
+    c = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+    DT, MT, ML = wgb.WholeGraphDataType, wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation
+    rows, dim, n = 3000, 64, 6000
+    rng = np.random.default_rng(4)
+    env = wgb.cached_env_fns()
+    emb = wgb.create_embedding(wgb.make_description([rows, dim], DT.DtFloat), c, MT.MtDistributed, ML.MlDevice)
+    opt = wgb.create_optimizer(wgb.WholeGraphOptimizerType.OptLazyAdam)
+    wgb.check(wgb.lib().wholegraph_embedding_set_optimizer(emb, opt), "set_optimizer")
+    table = wgb.embedding_tensor(emb)
+    init = rng.uniform(-1, 1, size=(rows, dim)).astype(np.float32)
+    gpu.scatter(torch.from_numpy(init).cuda(), torch.arange(rows, device="cuda", dtype=torch.int64), table)
+    w, state, beta = init.copy(), np.zeros((rows, 2 * dim), np.float32), np.ones((rows, 2), np.float32)
+    for step in range(2):
+        ids = rng.integers(0, rows, size=n).astype(np.int64)
+        ids[rng.permutation(n)[: n // 3]] = 1234
+        grads = rng.uniform(-1, 1, size=(n, dim)).astype(np.float32)
+        d_ids, d_grads = torch.from_numpy(ids).cuda(), torch.from_numpy(grads).cuda()
+        wi, wg = gpu.wrap_torch_tensor(d_ids), gpu.wrap_torch_tensor(d_grads)
+        wgb.EmbeddingGatherGradientApply(emb, wi, wg, False, 0.01, env, gpu.current_stream_int())
+        torch.cuda.synchronize()
+        wgb.destroy_wholegraph_tensor(wi)
+        wgb.destroy_wholegraph_tensor(wg)
+        uniq, sums = orc.dedup_gradients(ids, grads, block=256)
+        orc.optimizer_apply(2, uniq, sums, w, lr=0.01, state=state, v_offset=dim, beta12t=beta)
+    assert np.array_equal(_read_all(gpu, torch, table, rows, dim, torch.float32).cpu().numpy(), w)
+    assert np.array_equal(_read_all(gpu, torch, wgb.embedding_state(emb, "m"), rows, dim, torch.float32).cpu().numpy(), state[:, :dim])
+    assert np.array_equal(_read_all(gpu, torch, wgb.embedding_state(emb, "v"), rows, dim, torch.float32).cpu().numpy(), state[:, dim:])
+    assert np.array_equal(_read_all(gpu, torch, wgb.embedding_state(emb, "beta12t"), rows, 2, torch.float32).cpu().numpy(), beta)
+    wgb.destroy_embedding(emb)
+    wgb.lib().wholegraph_destroy_embedding_optimizer(opt)
+    wgb.destroy_communicator(c)
