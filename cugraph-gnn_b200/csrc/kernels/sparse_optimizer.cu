@@ -911,90 +911,114 @@ __global__ void __launch_bounds__(kThreads) merge_heads_kernel(const merge_param
 
 constexpr int kMergeFlight = 4;  // senders' rows in flight per lane (for two column groups)
 
+// One warp per touched row.  As in apply_kernel, a CTA first stages what a row's update depends
+// on for kThreads rows at once, one row per thread with coalesced and independent loads: the row
+// number, for every sender whether it holds the row and at which position of its list (bitmap word
+// and rank word), and the row's stepped beta powers.  A warp then finds everything in shared memory
+// and requests weights, state and every sender's sums row in one go.
 template <int OPT, typename W, int VEC>
 __global__ void __launch_bounds__(kThreads, 2) merge_apply_kernel(const merge_params p)
 {
+  extern __shared__ int32_t s_pos[];  // [world][kThreads]: position in sender q's group, -1 = not held
   __shared__ int64_t s_start[kMaxMergeRanks];
+  __shared__ int32_t s_row[kThreads];
+  __shared__ float s_beta[OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? kThreads : 1][2];
+  __shared__ int s_next;
   if (threadIdx.x < p.world) {
     int64_t c, s;
     read_group(p, threadIdx.x, &c, &s);
     s_start[threadIdx.x] = s;
   }
-  __syncthreads();
-  constexpr unsigned kFull  = 0xffffffffu;
-  const int lane            = threadIdx.x & 31;
-  const int64_t warp_global = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t warp_stride = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
-  const int heads           = *p.head_count;
-  W* weights                = static_cast<W*>(p.weights);
-  for (int64_t hd = warp_global; hd < heads; hd += warp_stride) {
-    const int row = p.heads[hd];
-    // lane q: does sender q hold this row, and where
-    const float* src = nullptr;
-    if (lane < p.world) {
-      const int64_t wi    = static_cast<int64_t>(lane) * p.words + (row >> 5);
-      const uint32_t word = p.bitmap[wi];
-      if ((word >> (row & 31)) & 1u) {
-        const int64_t pos = p.rank[wi] - p.rank[static_cast<int64_t>(lane) * p.words] +
-                            __popc(word & ((1u << (row & 31)) - 1u));
-        src = p.sender[lane].sums + (s_start[lane] + pos) * p.dim;
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane           = threadIdx.x & 31;
+  const int t              = threadIdx.x;
+  const int heads          = *p.head_count;
+  W* weights               = static_cast<W*>(p.weights);
+  apply_params ap{};  // the fields row_columns reads
+  ap.v_offset = p.v_offset, ap.h = p.h;
+  auto next_row = [&]() -> int {
+    int r = 0;
+    if (lane == 0) r = atomicAdd(&s_next, 1);
+    return __shfl_sync(kFull, r, 0);
+  };
+  for (int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kThreads; tile0 < heads;
+       tile0 += static_cast<int64_t>(gridDim.x) * kThreads) {
+    __syncthreads();  // the previous tile has been consumed (and s_start is in place)
+    const int64_t hd = tile0 + t;
+    int row          = -1;
+    if (hd < heads) {
+      row = p.heads[hd];
+      for (int q = 0; q < p.world; q++) {
+        const int64_t wi    = static_cast<int64_t>(q) * p.words + (row >> 5);
+        const uint32_t word = p.bitmap[wi];
+        int pos             = -1;
+        if ((word >> (row & 31)) & 1u)
+          pos = p.rank[wi] - p.rank[static_cast<int64_t>(q) * p.words] + __popc(word & ((1u << (row & 31)) - 1u));
+        s_pos[q * kThreads + t] = pos;
       }
-    }
-    unsigned senders = __ballot_sync(kFull, src != nullptr);
-    float beta1t = 0.f, beta2t = 0.f;
-    if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
-      // per-row running beta1^t, beta2^t: multiplied on every touch of the row
-      float2 v = make_float2(0.f, 0.f);
-      if (lane == 0) {
+      if (OPT == WHOLEGRAPH_OPT_LAZY_ADAM) {
+        // per-row running beta1^t, beta2^t: multiplied on every touch of the row
         float2* b = reinterpret_cast<float2*>(p.beta12t) + row;
-        v         = *b;
+        float2 v  = *b;
         v.x       = __fmul_rn(v.x, p.h.beta1);
         v.y       = __fmul_rn(v.y, p.h.beta2);
         *b        = v;
+        s_beta[t][0] = v.x, s_beta[t][1] = v.y;
       }
-      beta1t = __shfl_sync(kFull, v.x, 0);
-      beta2t = __shfl_sync(kFull, v.y, 0);
     }
-    W* w_row     = weights + static_cast<int64_t>(row) * p.weight_stride;
-    float* s_row = p.state != nullptr ? p.state + static_cast<int64_t>(row) * p.state_stride : nullptr;
-    apply_params ap{};  // the fields row_columns reads
-    ap.v_offset = p.v_offset, ap.h = p.h;
-    for (int cb = 0; cb < p.dim; cb += 64 * VEC) {
-      const int c0 = cb + lane * VEC, c1 = c0 + 32 * VEC;
-      const bool on0 = c0 < p.dim, on1 = c1 < p.dim;
-      float acc0[VEC] = {}, acc1[VEC] = {};
-      row_columns<OPT, W, VEC> x0, x1;
-      x0.load(ap, w_row, s_row, c0, on0);
-      x1.load(ap, w_row, s_row, c1, on1);
-      unsigned left = senders;
-      bool first    = true;
-      while (left != 0u) {
-        float v0[kMergeFlight][VEC], v1[kMergeFlight][VEC];
-        bool live[kMergeFlight];
+    s_row[t] = row;
+    if (t == 0) s_next = 0;
+    __syncthreads();
+    const int in_tile = static_cast<int>(heads - tile0 < kThreads ? heads - tile0 : kThreads);
+    for (int r = next_row(); r < in_tile; r = next_row()) {
+      const int urow   = s_row[r];
+      const float* src = nullptr;
+      if (lane < p.world) {
+        const int pos = s_pos[lane * kThreads + r];
+        if (pos >= 0) src = p.sender[lane].sums + (s_start[lane] + pos) * p.dim;
+      }
+      const unsigned senders = __ballot_sync(kFull, src != nullptr);
+      const float beta1t     = OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? s_beta[r][0] : 0.f;
+      const float beta2t     = OPT == WHOLEGRAPH_OPT_LAZY_ADAM ? s_beta[r][1] : 0.f;
+      W* w_row     = weights + static_cast<int64_t>(urow) * p.weight_stride;
+      float* s_rw  = p.state != nullptr ? p.state + static_cast<int64_t>(urow) * p.state_stride : nullptr;
+      for (int cb = 0; cb < p.dim; cb += 64 * VEC) {
+        const int c0 = cb + lane * VEC, c1 = c0 + 32 * VEC;
+        const bool on0 = c0 < p.dim, on1 = c1 < p.dim;
+        float acc0[VEC] = {}, acc1[VEC] = {};
+        row_columns<OPT, W, VEC> x0, x1;
+        x0.load(ap, w_row, s_rw, c0, on0);
+        x1.load(ap, w_row, s_rw, c1, on1);
+        unsigned left = senders;
+        bool first    = true;
+        while (left != 0u) {
+          float v0[kMergeFlight][VEC], v1[kMergeFlight][VEC];
+          bool live[kMergeFlight];
 #pragma unroll
-        for (int u = 0; u < kMergeFlight; u++) {
-          live[u]     = left != 0u;
-          const int q = live[u] ? __ffs(left) - 1 : 0;
-          if (live[u]) left &= left - 1u;
-          const float* g = reinterpret_cast<const float*>(
-            __shfl_sync(kFull, reinterpret_cast<unsigned long long>(src), q));
-          load_grad<VEC>(g + c0, live[u] && on0, v0[u]);
-          load_grad<VEC>(g + c1, live[u] && on1, v1[u]);
-        }
+          for (int u = 0; u < kMergeFlight; u++) {
+            live[u]     = left != 0u;
+            const int q = live[u] ? __ffs(left) - 1 : 0;
+            if (live[u]) left &= left - 1u;
+            const float* g = reinterpret_cast<const float*>(
+              __shfl_sync(kFull, reinterpret_cast<unsigned long long>(src), q));
+            load_grad<VEC>(g + c0, live[u] && on0, v0[u]);
+            load_grad<VEC>(g + c1, live[u] && on1, v1[u]);
+          }
 #pragma unroll
-        for (int u = 0; u < kMergeFlight; u++) {
-          if (live[u]) {
+          for (int u = 0; u < kMergeFlight; u++) {
+            if (live[u]) {
 #pragma unroll
-            for (int e = 0; e < VEC; e++) {
-              acc0[e] = first ? v0[u][e] : __fadd_rn(acc0[e], v0[u][e]);
-              acc1[e] = first ? v1[u][e] : __fadd_rn(acc1[e], v1[u][e]);
+              for (int e = 0; e < VEC; e++) {
+                acc0[e] = first ? v0[u][e] : __fadd_rn(acc0[e], v0[u][e]);
+                acc1[e] = first ? v1[u][e] : __fadd_rn(acc1[e], v1[u][e]);
+              }
+              first = false;
             }
-            first = false;
           }
         }
+        x0.update_and_store(ap, w_row, s_rw, c0, on0, acc0, beta1t, beta2t);
+        x1.update_and_store(ap, w_row, s_rw, c1, on1, acc1, beta1t, beta2t);
       }
-      x0.update_and_store(ap, w_row, s_row, c0, on0, acc0, beta1t, beta2t);
-      x1.update_and_store(ap, w_row, s_row, c1, on1, acc1, beta1t, beta2t);
     }
   }
 }
@@ -1027,11 +1051,14 @@ merge_layout merge_layout_for(int world, int64_t local_rows, int64_t entries_upp
 template <int OPT, typename W>
 void launch_merge_apply(const merge_params& p, bool vec4, cudaStream_t stream)
 {
-  const int ctas = sm_count() * 2;
+  // One CTA per tile of kThreads touched rows up to a few waves, then grid-stride; their number is
+  // device data, CTAs without a tile leave at once.
+  const int ctas     = sm_count() * 2 * 8;
+  const size_t smem  = static_cast<size_t>(p.world) * kThreads * sizeof(int32_t);
   if (vec4)
-    merge_apply_kernel<OPT, W, 4><<<ctas, kThreads, 0, stream>>>(p);
+    merge_apply_kernel<OPT, W, 4><<<ctas, kThreads, smem, stream>>>(p);
   else
-    merge_apply_kernel<OPT, W, 1><<<ctas, kThreads, 0, stream>>>(p);
+    merge_apply_kernel<OPT, W, 1><<<ctas, kThreads, smem, stream>>>(p);
 }
 
 template <typename W>

@@ -172,45 +172,56 @@ __device__ __forceinline__ uint32_t mix(uint32_t x)
 constexpr uint32_t kNoEntry    = 0xffffffffu;
 constexpr uint32_t kClaimedBit = 0x80000000u;
 
+constexpr int kHashItems = 8;                      // ids per thread
+constexpr int kHashTile  = kThreads * kHashItems;  // ids per CTA
+
+// Per-owner counts go through shared memory first: a CTA adds its 2048 ids' worth to the global
+// counters with one atomic per owner (one atomic per warp and owner on the same few global
+// addresses cost 0.3 ms for 4,194,304 ids).
 __global__ void __launch_bounds__(kThreads)
   insert_kernel(const void* ids, int is64, int64_t n, owner_bounds b, uint2* table, uint32_t table_mask,
                 uint32_t* entry_of, unsigned long long* owner_count)
 {
   __shared__ int64_t s_first[kMaxPartitionRanks + 1];
+  __shared__ int s_count[kMaxPartitionRanks];
   for (int i = threadIdx.x; i <= b.world; i += kThreads) s_first[i] = b.first_row[i];
+  for (int i = threadIdx.x; i < b.world; i += kThreads) s_count[i] = 0;
   __syncthreads();
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  int owner       = b.world;  // b.world: nothing to count
-  if (i < n) {
-    const int64_t id = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
-                            : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
-    uint32_t where   = kNoEntry;
-    if (id >= 0 && id < s_first[b.world]) {
-      const uint32_t key = static_cast<uint32_t>(id) + 1u;
-      uint32_t s         = mix(key) & table_mask;
-      bool claimed       = false;
-      for (;;) {
-        uint32_t seen = __ldcg(&table[s].x);
-        if (seen == 0u) {
-          seen = atomicCAS(&table[s].x, 0u, key);
+  const int lane     = threadIdx.x & 31;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kHashTile;
+#pragma unroll
+  for (int j = 0; j < kHashItems; j++) {
+    const int64_t i = base + j * kThreads + threadIdx.x;
+    int owner       = b.world;  // b.world: nothing to count
+    if (i < n) {
+      const int64_t id = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
+                              : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
+      uint32_t where   = kNoEntry;
+      if (id >= 0 && id < s_first[b.world]) {
+        const uint32_t key = static_cast<uint32_t>(id) + 1u;
+        uint32_t s         = mix(key) & table_mask;
+        bool claimed       = false;
+        bool found         = false;
+        while (!found) {
+          uint32_t seen = __ldcg(&table[s].x);
           if (seen == 0u) {
-            claimed = true;
-            break;
+            seen    = atomicCAS(&table[s].x, 0u, key);
+            claimed = seen == 0u;
           }
+          found = claimed || seen == key;
+          if (!found) s = (s + 1u) & table_mask;
         }
-        if (seen == key) break;
-        s = (s + 1u) & table_mask;
+        where = s | (claimed ? kClaimedBit : 0u);
+        if (claimed) owner = owner_of_row(id, s_first, b.world);
       }
-      where = s | (claimed ? kClaimedBit : 0u);
-      if (claimed) owner = owner_of_row(id, s_first, b.world);
+      entry_of[i] = where;
     }
-    entry_of[i] = where;
+    const unsigned peers = __match_any_sync(0xffffffffu, owner);
+    if (owner < b.world && lane == __ffs(peers) - 1) atomicAdd(&s_count[owner], __popc(peers));
   }
-  // one atomic per warp and owner
-  const unsigned peers = __match_any_sync(0xffffffffu, owner);
-  const int lane       = threadIdx.x & 31;
-  if (owner < b.world && lane == __ffs(peers) - 1)
-    atomicAdd(owner_count + owner, static_cast<unsigned long long>(__popc(peers)));
+  __syncthreads();
+  for (int o = threadIdx.x; o < b.world; o += kThreads)
+    if (s_count[o] != 0) atomicAdd(owner_count + o, static_cast<unsigned long long>(s_count[o]));
 }
 
 __global__ void starts_kernel(unsigned long long* owner_count, int world, int64_t* counts, int64_t* starts)
@@ -226,35 +237,56 @@ __global__ void starts_kernel(unsigned long long* owner_count, int world, int64_
   }
 }
 
+// Claimers take slots of their owner's group: positions inside the CTA first (shared memory),
+// then one reservation per owner and CTA on the global cursors.
 __global__ void __launch_bounds__(kThreads)
   place_kernel(const void* ids, int is64, int64_t n, owner_bounds b, uint2* table, const uint32_t* entry_of,
                unsigned long long* cursor, int64_t* unique_ids)
 {
   __shared__ int64_t s_first[kMaxPartitionRanks + 1];
+  __shared__ int s_count[kMaxPartitionRanks];
+  __shared__ unsigned long long s_base[kMaxPartitionRanks];
   for (int i = threadIdx.x; i <= b.world; i += kThreads) s_first[i] = b.first_row[i];
+  for (int i = threadIdx.x; i < b.world; i += kThreads) s_count[i] = 0;
   __syncthreads();
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  int owner       = b.world;
-  int64_t id      = -1;
-  uint32_t where  = kNoEntry;
-  if (i < n) {
-    where = entry_of[i];
-    if (where != kNoEntry && (where & kClaimedBit) != 0u) {
-      id    = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
-                   : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
-      owner = owner_of_row(id, s_first, b.world);
+  const int lane     = threadIdx.x & 31;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kHashTile;
+  int64_t id[kHashItems];
+  uint32_t where[kHashItems];
+  int owner[kHashItems], local[kHashItems];
+#pragma unroll
+  for (int j = 0; j < kHashItems; j++) {
+    const int64_t i = base + j * kThreads + threadIdx.x;
+    owner[j]        = b.world;
+    where[j]        = kNoEntry;
+    id[j]           = -1;
+    local[j]        = 0;
+    if (i < n) {
+      where[j] = entry_of[i];
+      if (where[j] != kNoEntry && (where[j] & kClaimedBit) != 0u) {
+        id[j]    = is64 ? __ldg(static_cast<const int64_t*>(ids) + i)
+                        : static_cast<int64_t>(__ldg(static_cast<const int*>(ids) + i));
+        owner[j] = owner_of_row(id[j], s_first, b.world);
+      }
     }
+    const unsigned peers = __match_any_sync(0xffffffffu, owner[j]);
+    const int leader     = __ffs(peers) - 1;
+    int first            = 0;
+    if (owner[j] < b.world && lane == leader) first = atomicAdd(&s_count[owner[j]], __popc(peers));
+    first    = __shfl_sync(0xffffffffu, first, leader);
+    local[j] = first + __popc(peers & ((1u << lane) - 1u));
   }
-  const unsigned peers = __match_any_sync(0xffffffffu, owner);
-  const int lane       = threadIdx.x & 31;
-  const int leader     = __ffs(peers) - 1;
-  unsigned long long base = 0;
-  if (owner < b.world && lane == leader) base = atomicAdd(cursor + owner, static_cast<unsigned long long>(__popc(peers)));
-  base = __shfl_sync(0xffffffffu, base, leader);
-  if (owner < b.world) {
-    const int64_t slot = static_cast<int64_t>(base) + __popc(peers & ((1u << lane) - 1u));
-    unique_ids[slot]   = id;
-    table[where & ~kClaimedBit].y = static_cast<uint32_t>(slot);
+  __syncthreads();
+  for (int o = threadIdx.x; o < b.world; o += kThreads)
+    s_base[o] = s_count[o] != 0 ? atomicAdd(cursor + o, static_cast<unsigned long long>(s_count[o])) : 0ull;
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kHashItems; j++) {
+    if (owner[j] < b.world) {
+      const int64_t slot = static_cast<int64_t>(s_base[owner[j]]) + local[j];
+      unique_ids[slot]   = id[j];
+      table[where[j] & ~kClaimedBit].y = static_cast<uint32_t>(slot);
+    }
   }
 }
 
@@ -326,11 +358,12 @@ void unique_by_owner(const void* ids, bool ids_are_64, int64_t n, const int64_t*
     b.world = world;
     for (int r = 0; r <= world; r++) b.first_row[r] = first_row[r];
     const unsigned blocks = static_cast<unsigned>((n + kThreads - 1) / kThreads);
-    insert_kernel<<<blocks, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, b, table, l.entries - 1, entry_of,
-                                                   owner_count);
+    const unsigned tiles  = static_cast<unsigned>((n + kHashTile - 1) / kHashTile);
+    insert_kernel<<<tiles, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, b, table, l.entries - 1, entry_of,
+                                                  owner_count);
     starts_kernel<<<1, 32, 0, stream>>>(owner_count, world, counts, starts);
-    place_kernel<<<blocks, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, b, table, entry_of, owner_count,
-                                                  unique_ids);
+    place_kernel<<<tiles, kThreads, 0, stream>>>(ids, ids_are_64 ? 1 : 0, n, b, table, entry_of, owner_count,
+                                                 unique_ids);
     inverse_kernel<<<blocks, kThreads, 0, stream>>>(n, table, entry_of, inverse);
     count_kernel_launch(4);
     WGB_LAUNCH_CHECK(stream);
