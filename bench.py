@@ -1245,8 +1245,10 @@ def main():
         line = run_sparse_adam(ctx, args.steps, args.warmup, want_ref=not args.no_extras)
     elif workload in ("c2", "c3", "c3-unique", "c4"):
         auto = args.workload == "auto"
-        if workload != "c2" and not multi:
-            raise SystemExit(f"the {workload} workload needs more than one GPU")
+        one_rank_exchange = os.environ.get("WG_SINGLE_RANK_EXCHANGE") == "1" and workload == "c4"
+        if workload != "c2" and not multi and not one_rank_exchange:
+            raise SystemExit(f"the {workload} workload needs more than one GPU (c4 also runs on one GPU with "
+                             "WG_SINGLE_RANK_EXCHANGE=1: the exchange code with the rank as its own peer, for profiling)")
         line = run_gather(ctx, workload, args.steps, args.warmup, want_e2e=not args.no_e2e,
                           want_parity=not args.no_parity, want_cpu=not args.no_cpu_baseline,
                           want_scatter=auto and not args.no_extras, want_ref=not args.no_extras,

@@ -117,10 +117,11 @@ void* plain_malloc(wholegraph_tensor_description_t* d, wholegraph_memory_allocat
   return c->ptr;
 }
 
-// ---- caching allocator: freed blocks are kept per (kind, power-of-two size) and reused.
+// ---- caching allocator: freed blocks are kept per (kind, device, power-of-two size) and reused.
 // Reuse is safe without a synchronize because a block goes back to the pool only when the op
 // that used it has finished enqueueing, and every consumer of the pool enqueues on the stream
-// it was given; callers that mix streams must order them themselves.
+// it was given; callers that mix streams must order them themselves.  Device blocks are only
+// handed back on the device they were allocated on.
 struct cache_pool {
   std::mutex mu;
   std::multimap<std::pair<int, size_t>, void*> free_blocks;
@@ -136,9 +137,16 @@ struct cache_pool {
 };
 struct cached_ctx {
   void* ptr   = nullptr;
-  int where   = 0;
+  int where   = 0;  // pool key: allocation kind and, for device memory, the device ordinal
   size_t size = 0;
 };
+
+int pool_kind(wholegraph_memory_allocation_type_t where)
+{
+  int dev = 0;
+  if (where == WHOLEGRAPH_MA_DEVICE) cudaGetDevice(&dev);
+  return static_cast<int>(where) * 1024 + dev;
+}
 
 size_t size_class(size_t bytes)
 {
@@ -171,7 +179,7 @@ void* cached_malloc(wholegraph_tensor_description_t* d, wholegraph_memory_alloca
   size_t cls = size_class(static_cast<size_t>(wholegraph_get_memory_size_from_tensor(d)));
   {
     std::lock_guard<std::mutex> lk(pool->mu);
-    auto it = pool->free_blocks.find({static_cast<int>(where), cls});
+    auto it = pool->free_blocks.find({pool_kind(where), cls});
     if (it != pool->free_blocks.end()) {
       c->ptr = it->second;
       pool->free_blocks.erase(it);
@@ -183,7 +191,7 @@ void* cached_malloc(wholegraph_tensor_description_t* d, wholegraph_memory_alloca
     std::lock_guard<std::mutex> lk(pool->mu);
     pool->all_blocks.push_back({c->ptr, static_cast<int>(where)});
   }
-  c->where = where;
+  c->where = pool_kind(where);
   c->size  = cls;
   return c->ptr;
 }

@@ -31,8 +31,11 @@ wholegraph_env_func_t* wholegraph_b200_get_default_env_func();
 
 /*
  * Allocator callbacks with a size-class free list: a buffer released by one op is handed to
- * the next one without touching the CUDA allocator.  Work that reuses a buffer must be ordered
- * on the stream(s) the ops were given.
+ * the next one without touching the CUDA allocator and without an event in between.  The
+ * contract: ops that draw from it are ordered on the streams they are given (one stream, or
+ * streams the caller orders itself); an op on stream B that starts while an op on stream A still
+ * runs may be handed A's buffer.  Device buffers are pooled per device and only handed back on the
+ * device that allocated them (the current device of the calling thread at the time of the call).
  */
 wholegraph_env_func_t* wholegraph_b200_get_cached_env_func();
 

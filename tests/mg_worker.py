@@ -336,9 +336,15 @@ def main():
                 wgb.destroy_wholegraph_tensor(wo)
                 assert np.array_equal(to_host(out), want_all[ids]), f"node-level cached gather {step} differs on rank {rank}"
                 wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
+            # something must have been cached: read all tag sets through the library (the tags live on the
+            # cache communicator; a small shard may sit in a page of a neighbour's GPU, where torch cannot
+            # wrap the pointer, but every rank of that communicator can gather from it)
             tags = wgb.embedding_cache_tensors(emb)[0]
-            lt = tu.local_shard_as_torch(tags)
-            assert int((lt.view(torch.int16) != 0).sum().item()) > 0, "nothing was cached"
+            sets = wgb.lib().wholegraph_tensor_get_tensor_description(tags).contents.sizes[0]
+            all_tags = torch.zeros((sets, 32), dtype=torch.int16, device="cuda")
+            tu.gather(tags, torch.arange(sets, device="cuda", dtype=torch.int64), all_tags, env)
+            torch.cuda.synchronize()
+            assert int((all_tags != 0).sum().item()) > 32, "nothing was cached"
             wgb.check(wgb.lib().wholegraph_communicator_barrier(comm), "barrier")
             wgb.destroy_embedding(emb)
             wgb.destroy_cache_policy(policy)
