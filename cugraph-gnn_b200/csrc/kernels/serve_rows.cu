@@ -29,6 +29,7 @@ struct serve_params {
   const char* shard;
   int64_t first_local_row, local_rows;
   int64_t shard_stride_bytes, row_bytes;
+  int interleave;
   int* status;
   serve_region region[kMaxServeRanks];
 };
@@ -68,20 +69,40 @@ __global__ void __launch_bounds__(kThreads, 4) serve_rows_kernel(const serve_par
   const int sub           = lane / lpr;
   const int col0          = lane % lpr;
   const int rows_per_pass = 32 / lpr;
-  const int64_t tiles       = (total + kTile - 1) / kTile;
+  // Order of the tiles.  Rotation: requester after requester.  Interleaved: tile u of requester k
+  // is unit u * world + k, so at every moment an owner's stores spread evenly over all requesters
+  // (and every requester receives from all owners at once), whatever the skew between the ranks.
+  int64_t tiles = (total + kTile - 1) / kTile;
+  if (p.interleave) {
+    int64_t longest = 0;
+    for (int k = 0; k < p.world; k++) longest = max(longest, s_prefix[k + 1] - s_prefix[k]);
+    tiles = (longest + kTile - 1) / kTile * p.world;
+  }
   const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * kWarps + warp;
   const int64_t warp_stride = static_cast<int64_t>(gridDim.x) * kWarps;
 
   for (int64_t tile = warp_global; tile < tiles; tile += warp_stride) {
     {
-      const int64_t i = tile * kTile + lane;
-      int64_t row     = -1;
-      char* dst       = nullptr;
-      if (i < total) {
-        int k = 0;
-        while (k + 1 < p.world && i >= s_prefix[k + 1]) k++;
+      int k = 0;
+      int64_t in_group;  // position within requester k's group
+      bool valid;
+      if (p.interleave) {
+        k        = static_cast<int>(tile % p.world);
+        in_group = tile / p.world * kTile + lane;
+        valid    = in_group < s_prefix[k + 1] - s_prefix[k];
+        if (!__any_sync(0xffffffffu, valid)) continue;
+      } else {
+        const int64_t i = tile * kTile + lane;
+        valid           = i < total;
+        if (valid)
+          while (k + 1 < p.world && i >= s_prefix[k + 1]) k++;
+        in_group = i - s_prefix[k];
+      }
+      int64_t row = -1;
+      char* dst   = nullptr;
+      if (valid) {
         const int q      = (p.me + 1 + k) % p.world;
-        const int64_t j  = s_start[k] + (i - s_prefix[k]);
+        const int64_t j  = s_start[k] + in_group;
         const int64_t id = __ldcg(p.region[q].ids + j);
         row              = id - p.first_local_row;
         if (row < 0 || row >= p.local_rows) {  // not a row of this shard: never dereferenced
@@ -151,6 +172,7 @@ void launch_serve_rows(const serve_rows_args& a, cudaStream_t stream)
   p.first_local_row = a.first_local_row, p.local_rows = a.local_rows;
   p.shard_stride_bytes = a.shard_stride_bytes, p.row_bytes = a.row_bytes;
   p.status = a.status;
+  p.interleave = a.interleave ? 1 : 0;
   for (int r = 0; r < a.world; r++) p.region[r] = a.region[r];
 
   static int sm_count = [] {

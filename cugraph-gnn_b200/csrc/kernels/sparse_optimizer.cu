@@ -249,7 +249,12 @@ struct row_columns {
 };
 
 constexpr int kTileRuns    = kThreads;  // runs whose metadata one CTA stages at a time, one per thread (64-run tiles measured slower: 1.26 against 1.18 ms per C5 step)
-constexpr int kApplyFlight = 8;         // duplicate rows a lane requests (for two column groups) before adding
+constexpr int kApplyFlight = 4;         // duplicate rows a lane requests (for two column groups) before adding
+// CTAs per SM of the two update kernels.  With 4 rows in flight they fit 80 registers without
+// spills, which buys a third CTA per SM (24 warps instead of 16); measured on the 2,097,152-row
+// Zipf(1.1) Lazy Adam step this beats 8 rows in flight at two CTAs (0.91 against 0.97 ms), the
+// update being bound by instruction issue and latency together, not by duplicate rows in flight.
+constexpr int kApplyCtas = 3;
 
 // Distinct rows with at most kDedupBlock duplicates: summed and applied here.  Longer runs are
 // only registered, with one partial-sum slot per block of kDedupBlock rows.
@@ -263,7 +268,7 @@ constexpr int kApplyFlight = 8;         // duplicate rows a lane requests (for t
 // (their list positions come 32 at a time from one coalesced load, handed out by shuffles).
 // VEC = 4: dim, strides and base pointers allow 16-byte accesses; VEC = 1 otherwise.
 template <int OPT, typename W, int VEC>
-__global__ void __launch_bounds__(kThreads, 2) apply_kernel(const apply_params p)
+__global__ void __launch_bounds__(kThreads, kApplyCtas) apply_kernel(const apply_params p)
 {
   __shared__ int32_t s_first[kTileRuns + 1];
   __shared__ uint32_t s_row[kTileRuns];
@@ -330,11 +335,12 @@ __global__ void __launch_bounds__(kThreads, 2) apply_kernel(const apply_params p
     __syncthreads();
 
     const int in_tile = static_cast<int>(runs - tile0 < kTileRuns ? runs - tile0 : kTileRuns);
-    for (;;) {
+    auto next_run = [&]() -> int {
       int r = 0;
       if (lane == 0) r = atomicAdd(&s_next, 1);
-      r = __shfl_sync(kFull, r, 0);
-      if (r >= in_tile) break;
+      return __shfl_sync(kFull, r, 0);
+    };
+    for (int r = next_run(); r < in_tile; r = next_run()) {
       const int first_pos = s_pos0[r];
       if (first_pos < 0) continue;
       const int64_t begin = s_first[r], end = s_first[r + 1];
@@ -705,7 +711,7 @@ int apply_grid(int64_t count)
   // waves.  The number of rows is only known on the device, so the grid covers the case that
   // every gradient row has its own id; CTAs without a tile leave at once.
   const int64_t tiles = (count + kTileRuns - 1) / kTileRuns;
-  return static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(sm_count()) * 2 * 8));
+  return static_cast<int>(std::min<int64_t>(tiles, static_cast<int64_t>(sm_count()) * kApplyCtas * 8));
 }
 
 struct owner_table {
@@ -909,7 +915,7 @@ __global__ void __launch_bounds__(kThreads) merge_heads_kernel(const merge_param
   }
 }
 
-constexpr int kMergeFlight = 4;  // senders' rows in flight per lane (for two column groups)
+constexpr int kMergeFlight = 3;  // senders' rows in flight per lane (for two column groups)
 
 // One warp per touched row.  As in apply_kernel, a CTA first stages what a row's update depends
 // on for kThreads rows at once, one row per thread with coalesced and independent loads: the row
@@ -917,7 +923,7 @@ constexpr int kMergeFlight = 4;  // senders' rows in flight per lane (for two co
 // and rank word), and the row's stepped beta powers.  A warp then finds everything in shared memory
 // and requests weights, state and every sender's sums row in one go.
 template <int OPT, typename W, int VEC>
-__global__ void __launch_bounds__(kThreads, 2) merge_apply_kernel(const merge_params p)
+__global__ void __launch_bounds__(kThreads, kApplyCtas) merge_apply_kernel(const merge_params p)
 {
   extern __shared__ int32_t s_pos[];  // [world][kThreads]: position in sender q's group, -1 = not held
   __shared__ int64_t s_start[kMaxMergeRanks];
@@ -1053,7 +1059,7 @@ void launch_merge_apply(const merge_params& p, bool vec4, cudaStream_t stream)
 {
   // One CTA per tile of kThreads touched rows up to a few waves, then grid-stride; their number is
   // device data, CTAs without a tile leave at once.
-  const int ctas     = sm_count() * 2 * 8;
+  const int ctas     = sm_count() * kApplyCtas * 8;
   const size_t smem  = static_cast<size_t>(p.world) * kThreads * sizeof(int32_t);
   if (vec4)
     merge_apply_kernel<OPT, W, 4><<<ctas, kThreads, smem, stream>>>(p);

@@ -427,6 +427,7 @@ static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph
   s.shard_stride_bytes = tab.stride * static_cast<int64_t>(es_tab);
   s.row_bytes          = static_cast<int64_t>(row_b);
   s.status             = comm->status_word;
+  s.interleave         = comm->tuning.serve_interleave != 0;
   int64_t bound        = 0;  // a requester asks one owner for at most as many rows as its list is long
   for (int r = 0; r < W; r++)
     bound += std::min(all[static_cast<size_t>(r) * wholegraph_comm_::kBoardValues], s.local_rows);
