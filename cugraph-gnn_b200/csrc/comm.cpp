@@ -197,11 +197,6 @@ exchange_tuning tuning_from_environment()
   t.sync_free       = flag("WG_SYNC_FREE", t.sync_free);
   t.serve_interleave = flag("WG_SERVE_INTERLEAVE", t.serve_interleave);
   t.single_rank_exchange = flag("WG_SINGLE_RANK_EXCHANGE", t.single_rank_exchange);
-  if (const char* ph = getenv("WG_SERVE_PHASES")) {
-    const int v    = atoi(ph);
-    t.serve_phases = v >= 4 ? 4 : v >= 2 ? 2 : 1;
-  }
-  if (const char* pb = getenv("WG_SERVE_PHASE_BYTES")) t.serve_phase_bytes = static_cast<int>(std::min<long long>(std::max<long long>(0, atoll(pb)), 1 << 30));
   const char* k     = getenv("WG_EXCHANGE_CHUNKS");
   t.exchange_chunks = k != nullptr ? std::min(std::max(0, atoi(k)), 16) : 0;
   return t;
@@ -309,7 +304,6 @@ void destroy_comm(wholegraph_comm_* comm)
   if (comm->pin_stage) cudaFreeHost(comm->pin_stage);
   if (comm->side_stream) cudaStreamDestroy(comm->side_stream);
   if (comm->xchg_stream) cudaStreamDestroy(comm->xchg_stream);
-  if (comm->fill_stream) cudaStreamDestroy(comm->fill_stream);
   for (auto e : comm->events) cudaEventDestroy(e);
   if (comm->nccl != nullptr) nccl_lib().CommDestroy(static_cast<ncclComm_t>(comm->nccl));
   delete comm;

@@ -29,11 +29,6 @@ struct exchange_tuning {
   int sync_free       = 1;  // WG_SYNC_FREE=0: distributed gathers exchange their counts through the host
   int serve_interleave = 0;  // WG_SERVE_INTERLEAVE=1: an owner serves its requesters' tiles in turn (stores spread over
                              // all peers at every moment) instead of requester after requester
-  int serve_phases    = 1;  // WG_SERVE_PHASES=2|4: the owners answer a distributed gather in that many launches (slots
-                            // j % phases == launch), each followed by a barrier, and the requester expands the rows of a
-                            // launch into its output on a second stream while the next launch's rows arrive
-  int serve_phase_bytes = 32 << 20;  // WG_SERVE_PHASE_BYTES: smaller gathers (largest request x row bytes) use one launch
-  // (all members are ints: ranks compare their values as raw bytes, which padding would spoil)
   int single_rank_exchange = 0;  // WG_SINGLE_RANK_EXCHANGE=1: a one-rank communicator runs the exchange code of the
                                  // distributed ops (with itself as its only peer) instead of the direct kernels,
                                  // so that this code can be tested on one GPU
@@ -65,7 +60,6 @@ struct wholegraph_comm_ {
   // Second stream on which the row exchange of a distributed op runs while the caller's
   // stream keeps gathering, and the events that fence the two.
   cudaStream_t xchg_stream = nullptr;
-  cudaStream_t fill_stream = nullptr;  // default priority, created on first use: work that fills gaps beside the caller's stream
   std::vector<cudaEvent_t> events;
   cudaEvent_t event(size_t i);  // i-th pooled event (created on demand, timing disabled)
 

@@ -35,7 +35,6 @@ struct row_copy_params {
   int src_select;
   int dst_select;
   int indices_are_64;
-  int64_t index_mask, index_match;
   // CHUNKED tables: the BY_INDEX side ignores src / dst and resolves rows through `chunks`;
   // chunk_offset_bytes is that side's storage offset.
   int64_t chunk_offset_bytes;
@@ -210,7 +209,6 @@ __global__ void __launch_bounds__(kRowCopyThreads, 4)
         if (need_index)
           id = p.indices_are_64 ? __ldg(static_cast<const int64_t*>(p.indices) + i)
                                 : static_cast<int64_t>(__ldg(static_cast<const int*>(p.indices) + i));
-        if (p.index_mask != 0 && (id & p.index_mask) != p.index_match) id = -1;
         if (need_pos) pos = __ldg(p.positions + i);
       }
       s_index[warp][lane]    = id;

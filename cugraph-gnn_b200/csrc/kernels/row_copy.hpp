@@ -67,8 +67,6 @@ struct row_copy_args {
   int64_t dim              = 0;        // elements per row
   const void* indices      = nullptr;  // int32 / int64 row ids; a negative id skips position i
   bool indices_are_64      = true;
-  int64_t index_mask       = 0;        // when non-zero, only ids with (id & index_mask) == index_match take part;
-  int64_t index_match      = 0;        // the other positions are skipped like negative ids
   const int64_t* positions = nullptr;  // for ROW_BY_POSITION
   chunked_table chunks;                // optional, BY_INDEX side only
   list_segments segments;              // optional; when n > 0, `count` must equal segments.total()

@@ -119,8 +119,6 @@ void launch_row_copy(const row_copy_args& a, cudaStream_t stream)
     p.dst_select       = ROW_BY_INDEX;
   }
   p.indices_are_64     = a.indices_are_64 ? 1 : 0;
-  p.index_mask         = a.index_mask;
-  p.index_match        = a.index_match;
   p.chunks             = a.chunks;
   p.segments           = a.segments;
   WGB_EXPECTS(a.segments.n == 0 || a.segments.total() == a.count, "segment list does not add up to count");

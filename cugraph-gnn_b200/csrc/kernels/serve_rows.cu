@@ -30,7 +30,6 @@ struct serve_params {
   int64_t first_local_row, local_rows;
   int64_t shard_stride_bytes, row_bytes;
   int interleave;
-  int phase_mask, phase;  // this launch answers the slots j with (j & phase_mask) == phase
   int* status;
   serve_region region[kMaxServeRanks];
 };
@@ -39,7 +38,7 @@ template <int BYTES>
 __global__ void __launch_bounds__(kThreads, 4) serve_rows_kernel(const serve_params p)
 {
   __shared__ int64_t s_prefix[kMaxServeRanks + 1];  // rows asked by the first k requesters (rotation order)
-  __shared__ int64_t s_start[kMaxServeRanks];         // slot of the first row this launch answers for requester k
+  __shared__ int64_t s_start[kMaxServeRanks];
   __shared__ int64_t s_id[kWarps][kTile];            // local row, or -1
   __shared__ char* s_dst[kWarps][kTile];
 
@@ -55,10 +54,8 @@ __global__ void __launch_bounds__(kThreads, 4) serve_rows_kernel(const serve_par
       atomicExch(p.status, 1);
       count = 0;
     }
-    // the slots of this launch's phase inside [start, start + count): every (phase_mask + 1)-th
-    const int64_t skip        = (p.phase - start) & p.phase_mask;
-    s_start[threadIdx.x]      = start + skip;
-    s_prefix[threadIdx.x + 1] = count > skip ? (count - skip + p.phase_mask) / (p.phase_mask + 1) : 0;
+    s_start[threadIdx.x]      = start;
+    s_prefix[threadIdx.x + 1] = count;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -105,7 +102,7 @@ __global__ void __launch_bounds__(kThreads, 4) serve_rows_kernel(const serve_par
       char* dst   = nullptr;
       if (valid) {
         const int q      = (p.me + 1 + k) % p.world;
-        const int64_t j  = s_start[k] + in_group * (p.phase_mask + 1);
+        const int64_t j  = s_start[k] + in_group;
         const int64_t id = __ldcg(p.region[q].ids + j);
         row              = id - p.first_local_row;
         if (row < 0 || row >= p.local_rows) {  // not a row of this shard: never dereferenced
@@ -152,8 +149,6 @@ void launch_serve_rows(const serve_rows_args& a, cudaStream_t stream)
 {
   WGB_EXPECTS(a.world >= 1 && a.world <= kMaxServeRanks, "world size %d exceeds %d", a.world, kMaxServeRanks);
   WGB_EXPECTS(a.status != nullptr && (a.shard != nullptr || a.local_rows == 0), "incomplete serve arguments");
-  WGB_EXPECTS(a.phase_count >= 1 && (a.phase_count & (a.phase_count - 1)) == 0 && a.phase >= 0 && a.phase < a.phase_count,
-              "bad serve phase %d of %d", a.phase, a.phase_count);
   if (a.rows_upper_bound <= 0 || a.row_bytes <= 0) return;
   // Widest vector that divides the row, the shard's stride and both first addresses.
   int bytes = 16;
@@ -178,7 +173,6 @@ void launch_serve_rows(const serve_rows_args& a, cudaStream_t stream)
   p.shard_stride_bytes = a.shard_stride_bytes, p.row_bytes = a.row_bytes;
   p.status = a.status;
   p.interleave = a.interleave ? 1 : 0;
-  p.phase_mask = a.phase_count - 1, p.phase = a.phase;
   for (int r = 0; r < a.world; r++) p.region[r] = a.region[r];
 
   static int sm_count = [] {
@@ -189,7 +183,7 @@ void launch_serve_rows(const serve_rows_args& a, cudaStream_t stream)
   }();
   // The real number of rows is device data; the grid covers the bound, a few waves at most, and
   // warps without a tile leave at once.
-  const int64_t tiles = (a.rows_upper_bound / a.phase_count + a.world + kTile - 1) / kTile;
+  const int64_t tiles = (a.rows_upper_bound + kTile - 1) / kTile;
   int64_t ctas        = (tiles + kWarps - 1) / kWarps;
   ctas                = std::max<int64_t>(1, std::min<int64_t>(ctas, static_cast<int64_t>(sm_count) * 4 * 8));
   switch (bytes) {

@@ -31,8 +31,6 @@ struct serve_rows_args {
   int64_t shard_stride_bytes = 0;       // bytes between rows of the shard
   int64_t row_bytes     = 0;            // bytes per row moved (and between rows of `rows`)
   int64_t rows_upper_bound = 0;         // no more than this many rows are asked of this rank in total
-  int phase_count       = 1;            // power of two: this launch serves the slots j with j % phase_count == phase
-  int phase             = 0;
   bool interleave       = false;        // serve the requesters' tiles in turn instead of requester after requester
   int* status           = nullptr;      // device word: set non-zero when a header or an id is out of range
 };

@@ -371,7 +371,6 @@ static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph
     supported = supported && v[4] != 0;
   }
   if (!supported) return false;
-  const int64_t capacity_asked = capacity;  // the largest request: the same number on every rank
   if (!ensure_peer_arena(comm, region_bytes(capacity, row_b), stream)) return false;
   // The arena is usually larger than asked for: every rank derives the same capacity from its size.
   {
@@ -433,39 +432,18 @@ static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph
   for (int r = 0; r < W; r++)
     bound += std::min(all[static_cast<size_t>(r) * wholegraph_comm_::kBoardValues], s.local_rows);
   s.rows_upper_bound = bound;
+  launch_serve_rows(s, stream);
+  timer.mark("serve");
+  comm->stream_barrier(stream);  // every owner's rows have landed
+  timer.mark("barrier");
 
-  row_copy_args expand;  // rows[inverse[i]] -> output row i, cast here; ids nobody owns leave their row untouched
-  expand.src = my_rows, expand.src_dt = tab.dtype, expand.src_stride = dim, expand.src_select = ROW_BY_INDEX;
-  expand.dst = out, expand.dst_dt = od.dtype, expand.dst_stride = od.stride, expand.dst_offset = od.storage_offset;
-  expand.dst_select = ROW_SEQUENTIAL, expand.dim = dim, expand.sm_hint = sms;
-  expand.indices = inverse, expand.indices_are_64 = true, expand.count = n;
-
-  // The number of launches follows from values every rank holds (largest request, row bytes,
-  // tuning), because every launch is followed by a collective barrier.
-  const int phases = capacity_asked * static_cast<int64_t>(row_b) >= comm->tuning.serve_phase_bytes
-                       ? comm->tuning.serve_phases : 1;
-  if (phases > 1 && comm->fill_stream == nullptr)
-    WGB_CUDA_CHECK(cudaStreamCreateWithFlags(&comm->fill_stream, cudaStreamNonBlocking));
-  s.phase_count = phases;
-  for (int ph = 0; ph < phases; ph++) {
-    s.phase = ph;
-    launch_serve_rows(s, stream);
-    timer.mark("serve");
-    comm->stream_barrier(stream);  // every owner's rows of this launch have landed
-    timer.mark("barrier");
-    if (n == 0) continue;
-    expand.index_mask = phases - 1, expand.index_match = ph;
-    if (ph + 1 < phases) {  // beside the next launch, whose rows go to other slots
-      WGB_CUDA_CHECK(cudaEventRecord(comm->event(ph), stream));
-      WGB_CUDA_CHECK(cudaStreamWaitEvent(comm->fill_stream, comm->event(ph), 0));
-      launch_row_copy(expand, comm->fill_stream);
-    } else {
-      launch_row_copy(expand, stream);
-      if (phases > 1) {
-        WGB_CUDA_CHECK(cudaEventRecord(comm->event(phases), comm->fill_stream));
-        WGB_CUDA_CHECK(cudaStreamWaitEvent(stream, comm->event(phases), 0));
-      }
-    }
+  if (n > 0) {
+    row_copy_args expand;  // rows[inverse[i]] -> output row i, cast here; ids nobody owns leave their row untouched
+    expand.src = my_rows, expand.src_dt = tab.dtype, expand.src_stride = dim, expand.src_select = ROW_BY_INDEX;
+    expand.dst = out, expand.dst_dt = od.dtype, expand.dst_stride = od.stride, expand.dst_offset = od.storage_offset;
+    expand.dst_select = ROW_SEQUENTIAL, expand.dim = dim, expand.sm_hint = sms;
+    expand.indices = inverse, expand.indices_are_64 = true, expand.count = n;
+    launch_row_copy(expand, stream);
   }
   WGB_CUDA_CHECK(cudaMemcpyAsync(comm->status_host, comm->status_word, sizeof(int), cudaMemcpyDeviceToHost, stream));
   if (comm->arena_idle != nullptr) WGB_CUDA_CHECK(cudaEventRecord(comm->arena_idle, stream));

@@ -373,13 +373,10 @@ def test_gather_from_a_handle_with_raw_pointers(gpu, wgb, orc, mem_name):
     wgb.destroy_communicator(comm)
 
 
-@pytest.mark.parametrize("switches", [{}, {"WG_SERVE_INTERLEAVE": "1"},
-                                      {"WG_SERVE_PHASES": "2", "WG_SERVE_PHASE_BYTES": "1"},
-                                      {"WG_SERVE_PHASES": "4", "WG_SERVE_PHASE_BYTES": "1", "WG_SERVE_INTERLEAVE": "1"},
-                                      {"WG_SYNC_FREE": "0"}, {"WG_PEER_EXCHANGE": "0"}, {"WG_GATHER_DEDUP": "0"},
+@pytest.mark.parametrize("switches", [{}, {"WG_SERVE_INTERLEAVE": "1"}, {"WG_SYNC_FREE": "0"}, {"WG_PEER_EXCHANGE": "0"},
+                                      {"WG_GATHER_DEDUP": "0"},
                                       {"WG_GATHER_DEDUP": "0", "WG_PEER_EXCHANGE": "0", "WG_EXCHANGE_CHUNKS": "3"}],
-                         ids=["sync-free", "sync-free-interleaved", "sync-free-two-launches", "sync-free-four-launches-interleaved",
-                              "host-counts", "nccl-rows", "keep-duplicates",
+                         ids=["sync-free", "sync-free-interleaved", "host-counts", "nccl-rows", "keep-duplicates",
                               "keep-duplicates-chunked"])
 @pytest.mark.parametrize("tab_dt,out_dt,dim", [(4, 4, 128), (2, 1, 33), (1, 2, 64), (6, 6, 5)])
 def test_distributed_exchange_code_on_one_rank(gpu, wgb, orc, monkeypatch, switches, tab_dt, out_dt, dim):
