@@ -195,7 +195,7 @@ exchange_tuning tuning_from_environment()
   t.gradient_presum = flag("WG_GRADIENT_PRESUM", t.gradient_presum);
   t.peer_gradient   = flag("WG_PEER_GRADIENT", t.peer_gradient);
   t.sync_free       = flag("WG_SYNC_FREE", t.sync_free);
-  t.serve_interleave = flag("WG_SERVE_INTERLEAVE", t.serve_interleave);
+  t.serve_bulk      = flag("WG_SERVE_BULK", t.serve_bulk);
   t.single_rank_exchange = flag("WG_SINGLE_RANK_EXCHANGE", t.single_rank_exchange);
   const char* k     = getenv("WG_EXCHANGE_CHUNKS");
   t.exchange_chunks = k != nullptr ? std::min(std::max(0, atoi(k)), 16) : 0;

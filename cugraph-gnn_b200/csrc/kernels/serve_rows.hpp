@@ -31,7 +31,9 @@ struct serve_rows_args {
   int64_t shard_stride_bytes = 0;       // bytes between rows of the shard
   int64_t row_bytes     = 0;            // bytes per row moved (and between rows of `rows`)
   int64_t rows_upper_bound = 0;         // no more than this many rows are asked of this rank in total
-  bool interleave       = false;        // serve the requesters' tiles in turn instead of requester after requester
+  bool bulk             = false;        // stage tiles of rows in shared memory with bulk asynchronous copies and send each
+                                        // tile with one bulk store (rows and strides must be multiples of 16 bytes, rows of
+                                        // 128 bytes to 16 KiB; other shapes take the register kernel whatever this says)
   int* status           = nullptr;      // device word: set non-zero when a header or an id is out of range
 };
 

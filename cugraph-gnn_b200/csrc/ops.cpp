@@ -392,9 +392,10 @@ static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph
     const int code     = *comm->status_host;
     *comm->status_host = 0;
     WGB_CUDA_CHECK(cudaMemsetAsync(comm->status_word, 0, sizeof(int), stream));
-    throw comm_error(format_string("an earlier distributed gather refused %s",
-                                   code == 1 ? "a request header that did not fit its region"
-                                             : "ids outside the shard they were sent to"));
+    throw comm_error(format_string("an earlier distributed gather %s",
+                                   code == 1   ? "refused a request header that did not fit its region"
+                                   : code == 2 ? "refused ids outside the shard they were sent to"
+                                               : "gave up waiting for its own bulk copies"));
   }
 
   phase_timer timer(stream);
@@ -427,7 +428,7 @@ static bool gather_distributed_sync_free(wholegraph_handle_* h, const wholegraph
   s.shard_stride_bytes = tab.stride * static_cast<int64_t>(es_tab);
   s.row_bytes          = static_cast<int64_t>(row_b);
   s.status             = comm->status_word;
-  s.interleave         = comm->tuning.serve_interleave != 0;
+  s.bulk               = comm->tuning.serve_bulk != 0;
   int64_t bound        = 0;  // a requester asks one owner for at most as many rows as its list is long
   for (int r = 0; r < W; r++)
     bound += std::min(all[static_cast<size_t>(r) * wholegraph_comm_::kBoardValues], s.local_rows);

@@ -373,10 +373,10 @@ def test_gather_from_a_handle_with_raw_pointers(gpu, wgb, orc, mem_name):
     wgb.destroy_communicator(comm)
 
 
-@pytest.mark.parametrize("switches", [{}, {"WG_SERVE_INTERLEAVE": "1"}, {"WG_SYNC_FREE": "0"}, {"WG_PEER_EXCHANGE": "0"},
+@pytest.mark.parametrize("switches", [{}, {"WG_SERVE_BULK": "1"}, {"WG_SYNC_FREE": "0"}, {"WG_PEER_EXCHANGE": "0"},
                                       {"WG_GATHER_DEDUP": "0"},
                                       {"WG_GATHER_DEDUP": "0", "WG_PEER_EXCHANGE": "0", "WG_EXCHANGE_CHUNKS": "3"}],
-                         ids=["sync-free", "sync-free-interleaved", "host-counts", "nccl-rows", "keep-duplicates",
+                         ids=["sync-free", "sync-free-bulk-copies", "host-counts", "nccl-rows", "keep-duplicates",
                               "keep-duplicates-chunked"])
 @pytest.mark.parametrize("tab_dt,out_dt,dim", [(4, 4, 128), (2, 1, 33), (1, 2, 64), (6, 6, 5)])
 def test_distributed_exchange_code_on_one_rank(gpu, wgb, orc, monkeypatch, switches, tab_dt, out_dt, dim):
@@ -424,5 +424,37 @@ def test_distributed_exchange_code_on_one_rank(gpu, wgb, orc, monkeypatch, switc
     want_table = table_np.copy()
     orc.scatter(rows_in, perm, want_table, rows_bf16=(out_dt == 4), table_bf16=(tab_dt == 4))
     assert np.array_equal(_to_host(torch, back, tab_dt).view(want_table.dtype), want_table)
+    wgb.destroy_wholegraph_tensor(t)
+    wgb.destroy_communicator(comm)
+
+
+@pytest.mark.parametrize("dim", [64, 128, 136, 512, 4096, 4104])
+def test_distributed_gather_with_bulk_copies_over_row_sizes(gpu, wgb, orc, monkeypatch, dim):
+    """WG_SERVE_BULK=1: the owner-side kernel stages tiles of rows in shared memory with bulk
+    asynchronous copies and sends each tile with one bulk store.  bf16 rows of 128 bytes to 8 KiB
+    (tiles of 32 down to 1 rows) and two widths the bulk form does not take (272 bytes is a
+    multiple of 16 but 8208 exceeds a buffer: the register kernel serves those), a list with
+    repeats, skipped positions and a group that ends inside a tile; against the oracle, bit for bit."""
+    import torch
+    MT, ML, DT = wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphDataType
+    monkeypatch.setenv("WG_SINGLE_RANK_EXCHANGE", "1")
+    monkeypatch.setenv("WG_SERVE_BULK", "1")
+    comm = wgb.create_communicator(wgb.UniqueId(), 0, 1)
+    rng = np.random.default_rng(dim)
+    rows = 20_011 if dim <= 512 else 3_001
+    table_np = _random_table(rng, orc, rows, dim, 4)
+    t = wgb.create_wholegraph_tensor(wgb.make_description([rows, dim], DT(4)), comm, MT.MtDistributed, ML.MlDevice)
+    gpu.write_local_shard(t, _to_device(torch, table_np, 4).contiguous())
+    for n in (1, 33, 2 * rows + 7):
+        idx = rng.integers(0, rows, size=n).astype(np.int64)
+        if n > 10:
+            idx[::41] = -1
+        sentinel = _random_table(rng, orc, n, dim, 4)
+        d_out = _to_device(torch, sentinel.copy(), 4)
+        gpu.gather(t, torch.from_numpy(idx).cuda(), d_out)
+        torch.cuda.synchronize()
+        want = sentinel.copy()
+        orc.gather(table_np, idx, out_dt=4, out=want, table_bf16=True)
+        assert np.array_equal(_to_host(torch, d_out, 4).view(want.dtype), want), f"n={n}"
     wgb.destroy_wholegraph_tensor(t)
     wgb.destroy_communicator(comm)
