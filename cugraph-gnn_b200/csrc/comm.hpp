@@ -27,8 +27,9 @@ struct exchange_tuning {
   int peer_gradient   = 0;  // WG_PEER_GRADIENT=1: gradient sums are stored into the owner's arena
   int exchange_chunks = 0;  // WG_EXCHANGE_CHUNKS=k: chunks of a pipelined NCCL exchange (0: automatic)
   int sync_free       = 1;  // WG_SYNC_FREE=0: distributed gathers exchange their counts through the host
-  int serve_bulk      = 0;  // WG_SERVE_BULK=1: the owner-side kernel of a distributed gather moves rows with bulk
-                            // asynchronous copies through shared memory (one store per tile of 32 rows)
+  int serve_bulk      = 1;  // WG_SERVE_BULK=0: the owner-side kernel of a distributed gather moves rows through
+                            // registers with 16-byte peer stores instead of bulk asynchronous copies through
+                            // shared memory (one store per tile of 32 rows)
   int single_rank_exchange = 0;  // WG_SINGLE_RANK_EXCHANGE=1: a one-rank communicator runs the exchange code of the
                                  // distributed ops (with itself as its only peer) instead of the direct kernels,
                                  // so that this code can be tested on one GPU

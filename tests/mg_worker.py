@@ -448,7 +448,7 @@ def main():
     # read again by a collective call, so one set of processes can run every variant in turn.
     switches = {"keepdups": {"WG_GATHER_DEDUP": "0"}, "nopresum": {"WG_GRADIENT_PRESUM": "0"},
                 "peerpush": {"WG_PEER_GRADIENT": "1"}, "nccl": {"WG_PEER_EXCHANGE": "0"},
-                "hostcounts": {"WG_SYNC_FREE": "0"}, "bulk": {"WG_SERVE_BULK": "1"}}
+                "hostcounts": {"WG_SYNC_FREE": "0"}, "registers": {"WG_SERVE_BULK": "0"}}
     inherited = {k: os.environ.get(k) for sw in switches.values() for k in sw}
     for scenario in scenarios:
         base, suffix = scenario, ""

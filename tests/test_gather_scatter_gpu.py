@@ -373,10 +373,10 @@ def test_gather_from_a_handle_with_raw_pointers(gpu, wgb, orc, mem_name):
     wgb.destroy_communicator(comm)
 
 
-@pytest.mark.parametrize("switches", [{}, {"WG_SERVE_BULK": "1"}, {"WG_SYNC_FREE": "0"}, {"WG_PEER_EXCHANGE": "0"},
+@pytest.mark.parametrize("switches", [{}, {"WG_SERVE_BULK": "0"}, {"WG_SYNC_FREE": "0"}, {"WG_PEER_EXCHANGE": "0"},
                                       {"WG_GATHER_DEDUP": "0"},
                                       {"WG_GATHER_DEDUP": "0", "WG_PEER_EXCHANGE": "0", "WG_EXCHANGE_CHUNKS": "3"}],
-                         ids=["sync-free", "sync-free-bulk-copies", "host-counts", "nccl-rows", "keep-duplicates",
+                         ids=["sync-free", "sync-free-register-kernel", "host-counts", "nccl-rows", "keep-duplicates",
                               "keep-duplicates-chunked"])
 @pytest.mark.parametrize("tab_dt,out_dt,dim", [(4, 4, 128), (2, 1, 33), (1, 2, 64), (6, 6, 5)])
 def test_distributed_exchange_code_on_one_rank(gpu, wgb, orc, monkeypatch, switches, tab_dt, out_dt, dim):
@@ -430,7 +430,7 @@ def test_distributed_exchange_code_on_one_rank(gpu, wgb, orc, monkeypatch, switc
 
 @pytest.mark.parametrize("dim", [64, 128, 136, 512, 4096, 4104])
 def test_distributed_gather_with_bulk_copies_over_row_sizes(gpu, wgb, orc, monkeypatch, dim):
-    """WG_SERVE_BULK=1: the owner-side kernel stages tiles of rows in shared memory with bulk
+    """The owner-side kernel of the default path stages tiles of rows in shared memory with bulk
     asynchronous copies and sends each tile with one bulk store.  bf16 rows of 128 bytes to 8 KiB
     (tiles of 32 down to 1 rows) and two widths the bulk form does not take (272 bytes is a
     multiple of 16 but 8208 exceeds a buffer: the register kernel serves those), a list with
@@ -438,7 +438,6 @@ def test_distributed_gather_with_bulk_copies_over_row_sizes(gpu, wgb, orc, monke
     import torch
     MT, ML, DT = wgb.WholeGraphMemoryType, wgb.WholeGraphMemoryLocation, wgb.WholeGraphDataType
     monkeypatch.setenv("WG_SINGLE_RANK_EXCHANGE", "1")
-    monkeypatch.setenv("WG_SERVE_BULK", "1")
     comm = wgb.create_communicator(wgb.UniqueId(), 0, 1)
     rng = np.random.default_rng(dim)
     rows = 20_011 if dim <= 512 else 3_001

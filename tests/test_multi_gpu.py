@@ -24,7 +24,7 @@ def _device_count():
 # the reference does, -hostcounts exchanges the counts of a distributed gather through the host,
 # -nccl moves rows by NCCL instead of peer stores, -nopresum routes every gradient row (one
 # summation chain per id), -peerpush writes gradient sums straight into the owner's arena region.
-SCENARIOS = ["continuous", "distributed", "distributed-keepdups", "distributed-hostcounts", "distributed-nccl", "distributed-bulk", "unequal-bulk", "chunked",
+SCENARIOS = ["continuous", "distributed", "distributed-keepdups", "distributed-hostcounts", "distributed-nccl", "distributed-registers", "unequal-registers", "chunked",
              "optimizer", "optimizer-nopresum", "optimizer-peerpush", "cache", "fileio", "unequal", "unequal-nccl",
              "unequal-keepdups", "roundrobin", "hosttable", "nodecache", "stated-size"]
 
