@@ -915,15 +915,25 @@ __global__ void __launch_bounds__(kThreads) merge_heads_kernel(const merge_param
   }
 }
 
-constexpr int kMergeFlight = 3;  // senders' rows in flight per lane (for two column groups)
+// Senders' rows in flight per lane (for two column groups) and CTAs per SM, measured on the
+// 2,097,152-row Lazy Adam step: with one rank (sums in local memory) 3 rows in flight at 3 CTAs
+// per SM (80 registers, no spill) take 1.09 ms against 1.25 ms for 4 rows at 2 CTAs; with eight
+// ranks (most sums read over NVLink, hot rows held by every sender) it is the other way round,
+// 1.59 against 1.65 ms - fewer round trips per row beat more warps.
+struct merge_shape_local {
+  static constexpr int kFlight = 3, kCtas = 3;
+};
+struct merge_shape_peers {
+  static constexpr int kFlight = 4, kCtas = 2;
+};
 
 // One warp per touched row.  As in apply_kernel, a CTA first stages what a row's update depends
 // on for kThreads rows at once, one row per thread with coalesced and independent loads: the row
 // number, for every sender whether it holds the row and at which position of its list (bitmap word
 // and rank word), and the row's stepped beta powers.  A warp then finds everything in shared memory
 // and requests weights, state and every sender's sums row in one go.
-template <int OPT, typename W, int VEC>
-__global__ void __launch_bounds__(kThreads, kApplyCtas) merge_apply_kernel(const merge_params p)
+template <int OPT, typename W, int VEC, typename SHAPE>
+__global__ void __launch_bounds__(kThreads, SHAPE::kCtas) merge_apply_kernel(const merge_params p)
 {
   extern __shared__ int32_t s_pos[];  // [world][kThreads]: position in sender q's group, -1 = not held
   __shared__ int64_t s_start[kMaxMergeRanks];
@@ -998,10 +1008,10 @@ __global__ void __launch_bounds__(kThreads, kApplyCtas) merge_apply_kernel(const
         unsigned left = senders;
         bool first    = true;
         while (left != 0u) {
-          float v0[kMergeFlight][VEC], v1[kMergeFlight][VEC];
-          bool live[kMergeFlight];
+          float v0[SHAPE::kFlight][VEC], v1[SHAPE::kFlight][VEC];
+          bool live[SHAPE::kFlight];
 #pragma unroll
-          for (int u = 0; u < kMergeFlight; u++) {
+          for (int u = 0; u < SHAPE::kFlight; u++) {
             live[u]     = left != 0u;
             const int q = live[u] ? __ffs(left) - 1 : 0;
             if (live[u]) left &= left - 1u;
@@ -1011,7 +1021,7 @@ __global__ void __launch_bounds__(kThreads, kApplyCtas) merge_apply_kernel(const
             load_grad<VEC>(g + c1, live[u] && on1, v1[u]);
           }
 #pragma unroll
-          for (int u = 0; u < kMergeFlight; u++) {
+          for (int u = 0; u < SHAPE::kFlight; u++) {
             if (live[u]) {
 #pragma unroll
               for (int e = 0; e < VEC; e++) {
@@ -1059,12 +1069,17 @@ void launch_merge_apply(const merge_params& p, bool vec4, cudaStream_t stream)
 {
   // One CTA per tile of kThreads touched rows up to a few waves, then grid-stride; their number is
   // device data, CTAs without a tile leave at once.
-  const int ctas     = sm_count() * kApplyCtas * 8;
+  const bool peers   = p.world > 1;
+  const int ctas     = sm_count() * (peers ? merge_shape_peers::kCtas : merge_shape_local::kCtas) * 8;
   const size_t smem  = static_cast<size_t>(p.world) * kThreads * sizeof(int32_t);
-  if (vec4)
-    merge_apply_kernel<OPT, W, 4><<<ctas, kThreads, smem, stream>>>(p);
+  if (vec4 && peers)
+    merge_apply_kernel<OPT, W, 4, merge_shape_peers><<<ctas, kThreads, smem, stream>>>(p);
+  else if (vec4)
+    merge_apply_kernel<OPT, W, 4, merge_shape_local><<<ctas, kThreads, smem, stream>>>(p);
+  else if (peers)
+    merge_apply_kernel<OPT, W, 1, merge_shape_peers><<<ctas, kThreads, smem, stream>>>(p);
   else
-    merge_apply_kernel<OPT, W, 1><<<ctas, kThreads, smem, stream>>>(p);
+    merge_apply_kernel<OPT, W, 1, merge_shape_local><<<ctas, kThreads, smem, stream>>>(p);
 }
 
 template <typename W>
