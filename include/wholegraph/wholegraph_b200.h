@@ -173,7 +173,7 @@ int wholegraph_b200_exchange_chunk_count(const int64_t* matrix, int world, size_
 
 /*
  * Read the WG_* tuning variables of the distributed ops again (WG_PEER_EXCHANGE, WG_GATHER_DEDUP,
- * WG_GRADIENT_PRESUM, WG_PEER_GRADIENT, WG_EXCHANGE_CHUNKS, WG_SYNC_FREE).  They are read when a
+ * WG_GRADIENT_PRESUM, WG_PEER_GRADIENT, WG_EXCHANGE_CHUNKS, WG_SYNC_FREE, WG_SERVE_BULK).  They are read when a
  * communicator is created; a process that changes them afterwards calls this on every rank
  * (collective, blocking).  WHOLEGRAPH_LOGIC_ERROR when the ranks do not agree, the check the
  * reference applies to the parameters of its collective calls
