@@ -264,13 +264,13 @@ __global__ void __launch_bounds__(kBulkThreads, 2) serve_rows_bulk_kernel(const 
       atomicExch(p.status, 3);
       return false;
     }
+    // A tile with an id that is not this shard's is not sent at all: the status word already says
+    // so and the requester's next call fails with it.
     const unsigned whole = rows >= 32 ? kFull : ((1u << rows) - 1u);
-    if (present == whole) {
-      if (lane == 0) bulk_store_tile(dst, buf, static_cast<uint32_t>(rows) * row_bytes);
-    } else if ((present >> lane) & 1u) {  // slots with foreign ids keep what they hold
-      bulk_store_tile(dst + static_cast<int64_t>(lane) * row_bytes, buf + static_cast<size_t>(lane) * row_bytes, row_bytes);
+    if (lane == 0) {
+      if (present == whole) bulk_store_tile(dst, buf, static_cast<uint32_t>(rows) * row_bytes);
+      bulk_commit();  // one group per tile, sent or not, so that the buffer bookkeeping stays uniform
     }
-    bulk_commit();  // every lane, every tile: the groups of all lanes advance together
     return true;
   };
 
@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(kBulkThreads, 2) serve_rows_bulk_kernel(const 
   for (int64_t tile = warp_global; tile < tiles; tile += warp_stride, it++) {
     const int st = it % kBulkStages;
     // the store that last read this buffer (two tiles ago in issue order) has read it
-    if (it >= kBulkStages) bulk_wait_sources_read<1>();
+    if (it >= kBulkStages && lane == 0) bulk_wait_sources_read<1>();
     __syncwarp();
     int rows;
     char* dst;
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(kBulkThreads, 2) serve_rows_bulk_kernel(const 
   // Loads may still be on their way into this warp's buffers: give them the same limit once more
   // before the shared memory goes away.
   if (in_flight >= 0) mbarrier_wait_bounded(&s_bar[warp][in_flight % kBulkStages], (in_flight / kBulkStages) & 1);
-  bulk_wait_all();
+  if (lane == 0) bulk_wait_all();
 }
 }  // namespace
 

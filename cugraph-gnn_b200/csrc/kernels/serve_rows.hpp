@@ -41,8 +41,9 @@ struct serve_rows_args {
 // neighbours first, itself last) read counts[me] and starts[me] from q's header, then copy row
 // ids[starts + j] of the local shard to rows[starts + j] of q's region - a peer load of the id, a
 // local load of the row, a peer store of the row.  Nothing here depends on the host knowing the
-// counts.  Ids outside the local shard and headers that do not fit the region are skipped and
-// reported through `status`.  Enqueued on `stream`.
+// counts.  Ids outside the local shard (in the bulk form: the tile of up to 32 slots holding one)
+// and headers that do not fit the region are skipped and reported through `status`: 1 header,
+// 2 id, 3 a bulk copy that did not complete within the wait limit.  Enqueued on `stream`.
 void launch_serve_rows(const serve_rows_args& a, cudaStream_t stream);
 
 }  // namespace wgb
