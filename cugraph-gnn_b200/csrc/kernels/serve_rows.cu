@@ -350,12 +350,9 @@ void launch_serve_rows(const serve_rows_args& a, cudaStream_t stream)
     // One resident wave of CTAs, every warp walking its tiles with its own three buffers.
     p.tile_rows = static_cast<int>(std::min<int64_t>(32, kBulkStageBytes / a.row_bytes));
     constexpr size_t smem = static_cast<size_t>(kBulkWarps) * kBulkStages * kBulkStageBytes;
-    static const bool configured = [] {
-      WGB_CUDA_CHECK(cudaFuncSetAttribute(serve_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-      return true;
-    }();
-    (void)configured;
+    // per device, so set on every launch (a process may drive more than one GPU)
+    WGB_CUDA_CHECK(cudaFuncSetAttribute(serve_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(smem)));
     const int64_t tiles = a.rows_upper_bound / p.tile_rows + a.world;
     const int64_t ctas  = std::max<int64_t>(1, std::min<int64_t>((tiles + kBulkWarps - 1) / kBulkWarps,
                                                                   static_cast<int64_t>(sm_count) * 2));
